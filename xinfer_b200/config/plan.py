@@ -34,10 +34,26 @@ class PartSpec:
 
 
 @dataclass(frozen=True)
+class RopeScaling:
+    """Slower turning for long wavelengths (the rule of Llama 3.1): a pair whose wavelength
+    ``2 pi / f`` is shorter than ``original / high`` keeps its frequency f, one longer than
+    ``original / low`` turns at ``f / factor``, and between the two the frequency is
+    ``(1 - s) f / factor + s f`` with ``s = (original / wavelength - low) / (high - low)``."""
+
+    factor: float
+    low: float
+    high: float
+    original: float
+
+
+@dataclass(frozen=True)
 class RopeSpec(PartSpec):
     """Rotary position encoding over the first ``rotary_dim`` channels of each head.
 
     ``layout`` is "neox" (channel j pairs with j + rotary_dim/2) or "interleaved" (2j with 2j+1).
+    ``scaling`` changes the frequencies (None: ``theta^(-2j / rotary_dim)`` as they are).
+    ``tables`` False: no cos/sin table is built; kernels take the frequencies and form
+    ``position * frequency`` in float32 themselves, so no longest position has to be known.
     """
 
     head_dim: int = 0
@@ -45,6 +61,8 @@ class RopeSpec(PartSpec):
     theta: float = 10000.0
     max_positions: int = 0
     layout: str = "neox"
+    scaling: Optional[RopeScaling] = None
+    tables: bool = True
 
 
 @dataclass(frozen=True)
@@ -53,6 +71,10 @@ class NormSpec(PartSpec):
     eps: float = 1e-6
     # weight enters as (offset + w): 0 for plain RMSNorm, 1 for the "(1 + w)" family
     weight_offset: float = 0.0
+    # the tensor's name after the part's prefix ("" where the prefix is the whole name)
+    weight_name: str = "weight"
+    # how the random-weights mode draws the weight: "norm" (around one) or "around_zero"
+    init: str = "norm"
 
 
 @dataclass(frozen=True)
@@ -67,6 +89,45 @@ class AttentionSpec(PartSpec):
     rope: Optional[RopeSpec] = None
     # a query at position p sees keys j with p - window < j <= p; None = all earlier keys
     window: Optional[int] = None
+    # size of a value head (None: head_dim)
+    v_head_dim: Optional[int] = None
+    # q/k norm: with a learned weight per channel or without; before the rotation or after it
+    qk_norm_weight: bool = True
+    qk_norm_after_rope: bool = False
+    # the scores of all heads for one (query, key) pair are mixed by a learned [heads, heads] matrix
+    # before the softmax: score_h <- sum_g talk[h, g] score_g
+    talking_heads: bool = False
+    # the softmax has one more entry of score 0 that carries no value: p_j = e^s_j / (1 + sum e^s)
+    sink: bool = False
+    # tensor names of the q, k, v, output (and talk) matrices after the part's prefix; None: the
+    # "q_proj.weight" family
+    names: Optional[Tuple[str, ...]] = None
+
+    @property
+    def value_dim(self) -> int:
+        return self.head_dim if self.v_head_dim is None else self.v_head_dim
+
+
+@dataclass(frozen=True)
+class GatedRecurrenceSpec(PartSpec):
+    """A recurrence over ``width`` channels whose gates read only the current token (minGRU):
+    z = sigmoid(W_z h + b_z), u = W_x h + b_x, candidate c = u + 1/2 where u >= 0 and sigmoid(u)
+    elsewhere, state S <- (1 - z) S + z c per channel (float32, zero at a sequence's start),
+    output W_o (S * silu(W_g h))."""
+
+    hidden: int = 0
+    width: int = 0
+
+
+@dataclass(frozen=True)
+class ParallelMixerSpec(PartSpec):
+    """Two mixers that read the same input; the result is left_scale * left + right_scale * right."""
+
+    hidden: int = 0
+    left: Optional[PartSpec] = None
+    right: Optional[PartSpec] = None
+    left_scale: float = 1.0
+    right_scale: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -74,6 +135,19 @@ class FeedForwardSpec(PartSpec):
     hidden: int = 0
     intermediate: int = 0
     activation: str = "silu"
+    eps: float = 1e-6      # of activations that norm (polynorm)
+
+
+@dataclass(frozen=True)
+class ExpertTableSpec(PartSpec):
+    """``experts`` small SiLU-gated feed-forwards of which every token uses ``top``, named by a
+    table over token ids (no router); each chosen expert has weight 1 / top."""
+
+    hidden: int = 0
+    intermediate: int = 0
+    experts: int = 0
+    top: int = 1
+    vocab: int = 0
 
 
 @dataclass(frozen=True)
@@ -201,6 +275,8 @@ class ModelPlan:
     # logits = logit_softcap * tanh(logits / logit_softcap); None = off
     logit_scale: Optional[float] = None
     logit_softcap: Optional[float] = None
+    # the residual stream's dtype ("float32"); None = the engine's dtype
+    residual_dtype: Optional[str] = None
     # standard deviations used by the random-weights mode
     init_std: float = 0.02
     norm_init_std: float = 0.1
@@ -210,6 +286,8 @@ class ModelPlan:
             raise ValueError("a model plan needs at least one block")
         for b in self.blocks:
             b.validate()
+        if self.residual_dtype not in (None, "float32"):
+            raise ValueError(f"residual_dtype must be None or 'float32', got {self.residual_dtype!r}")
         if self.logit_softcap is not None and not (self.logit_softcap > 0):
             raise ValueError(f"logit_softcap must be positive, got {self.logit_softcap}")
         for pos, run in enumerate(self.runs):

@@ -67,6 +67,8 @@ def config_from_dict(raw: Mapping[str, Any]):
     """Choose the architecture by ``architectures`` (exactly one entry, as the reference requires,
     src/core/engine.rs:166-169) and return (entry, typed config)."""
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]       # some model folders name their one architecture under this key
     if not isinstance(archs, (list, tuple)) or len(archs) != 1 or not isinstance(archs[0], str):
         raise ConfigError(f"config key 'architectures' must be a list with exactly one name, got {archs!r}")
     entry = architecture_entry(archs[0])
@@ -78,9 +80,10 @@ def load_config(model_dir: str):
 
 
 def _register_builtin() -> None:
-    # the one architecture this engine ships; others are added by their own modules the same way
     from .qwen3 import Qwen3Config
+    from .tidarax import TidaraxConfig
     register_architecture(Qwen3Config.ARCHITECTURE, Qwen3Config.from_dict, lambda c: c.plan())
+    register_architecture(TidaraxConfig.ARCHITECTURE, TidaraxConfig.from_dict, lambda c: c.plan())
 
 
 _register_builtin()

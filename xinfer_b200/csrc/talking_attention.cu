@@ -1,0 +1,421 @@
+// Attention whose heads talk to each other before the softmax, over the paged cache.
+//
+//   raw_g[i, j]  = scale * q_g[i] . k_kv(g)[j]                    every query head g
+//   s_h[i, j]    = sum_g talk[h, g] * raw_g[i, j]                 (talk absent: s = raw)
+//   p_h[i, j]    = exp(s_h[i, j]) / (sink + sum_j' exp(s_h[i, j']))   sink = 1 with a silent extra entry of
+//                                                                 score 0, else 0;  j' over the keys i sees
+//   o_h[i]       = out_scale * sum_j p_h[i, j] v_kv(h)[j]
+//
+// A key is seen by the query at position p when max(0, p - window + 1) <= j <= p (window <= 0: from 0).
+// Because every head's score of a (query, key) pair enters every head's softmax, a block takes all
+// heads of a tile of queries.  Scores, the mix, the softmax and the value sum are float32 in both
+// storage types.  Also here: the kernel that prepares a step's queries, keys and values (rotation,
+// per-head norm before or after it, page write) with heads of different key and value sizes.
+#include "common.cuh"
+
+// ------------------------------------------------------------------------------------------
+// qkv[t] = [heads x d | kv_heads x d | kv_heads x dv].  Per q/k head, in this order:
+//   norm_mode 1: x <- x / rms(x) * w      (w absent: 1)
+//   rotation of the first `rot` channels by position * inv_freq[pair]  (inv_freq absent: none)
+//   norm_mode 2: x <- x / rms(x) * w
+// q goes to q_out[t, h], k and v into their pages ([page, kv_head, slot, d] and [.., dv]).
+// One block per token, one warp per head at a time; the angles' cos/sin are formed once per token.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                   const T* __restrict__ qkv, const float* __restrict__ q_w, const float* __restrict__ k_w,
+                                   const float* __restrict__ inv_freq, const int* __restrict__ positions,
+                                   const int* __restrict__ req_of_token, const int* __restrict__ block_table,
+                                   int table_stride, int nh, int nkv, int d, int dv, int rot, int interleaved, int norm_mode,
+                                   int page_size, int num_pages, float eps, int write_kv, int* err) {
+    extern __shared__ float sm[];
+    const int half = rot / 2;
+    float* cs = sm;                 // [half]
+    float* sn = sm + half;          // [half]
+    const int nwarps = blockDim.x >> 5, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    float* xs = sm + 2 * half + (size_t)warp * d;   // this warp's head
+    const int t = blockIdx.x;
+    const int pos = positions[t];
+    const int b = req_of_token[t];
+    if (inv_freq) {
+        for (int j = threadIdx.x; j < half; j += blockDim.x) {
+            const float a = (float)pos * inv_freq[j];
+            float s, c;
+            sincosf(a, &s, &c);
+            cs[j] = c;
+            sn[j] = s;
+        }
+    }
+    __syncthreads();
+    long long kv_row = -1;
+    if (write_kv && b >= 0) {
+        const int page = block_table[(size_t)b * table_stride + pos / page_size];
+        if (page < 0 || page >= num_pages) {
+            if (threadIdx.x == 0) atomicOr(err, XB_ERR_BAD_PAGE);
+        } else {
+            kv_row = (long long)page * nkv * page_size + (pos % page_size);
+        }
+    }
+    const size_t row_len = (size_t)(nh + nkv) * d + (size_t)nkv * dv;
+    const T* row = qkv + (size_t)t * row_len;
+    for (int h = warp; h < nh + 2 * nkv; h += nwarps) {
+        if (h >= nh + nkv) {      // a value head: copy
+            if (kv_row < 0) continue;
+            const int g = h - nh - nkv;
+            const T* x = row + (size_t)(nh + nkv) * d + (size_t)g * dv;
+            T* dst = v_cache + (size_t)(kv_row + (long long)g * page_size) * dv;
+            for (int i = lane; i < dv; i += 32) dst[i] = x[i];
+            continue;
+        }
+        const bool is_q = h < nh;
+        if (!is_q && kv_row < 0) continue;
+        const T* x = row + (size_t)h * d;
+        T* dst = is_q ? q_out + ((size_t)t * nh + h) * d
+                      : k_cache + (size_t)(kv_row + (long long)(h - nh) * page_size) * d;
+        const float* nw = is_q ? q_w : k_w;
+        float ss = 0.f;
+        for (int i = lane; i < d; i += 32) {
+            const float v = to_f32<T>(x[i]);
+            xs[i] = v;
+            ss += v * v;
+        }
+        __syncwarp();
+        if (norm_mode == 1) {
+            const float inv = 1.f / sqrtf(warp_sum(ss) / (float)d + eps);
+            for (int i = lane; i < d; i += 32) xs[i] = xs[i] * inv * (nw ? nw[i] : 1.f);
+            __syncwarp();
+        }
+        if (inv_freq) {
+            for (int j = lane; j < half; j += 32) {
+                const int i0 = interleaved ? 2 * j : j, i1 = interleaved ? 2 * j + 1 : j + half;
+                const float u = xs[i0], v = xs[i1];
+                xs[i0] = u * cs[j] - v * sn[j];
+                xs[i1] = v * cs[j] + u * sn[j];
+            }
+            __syncwarp();
+        }
+        if (norm_mode == 2) {
+            ss = 0.f;
+            for (int i = lane; i < d; i += 32) ss += xs[i] * xs[i];
+            const float inv = 1.f / sqrtf(warp_sum(ss) / (float)d + eps);
+            for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(xs[i] * inv * (nw ? nw[i] : 1.f));
+        } else {
+            for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(xs[i]);
+        }
+        __syncwarp();
+    }
+}
+
+XB_EXPORT int xb_qkv_prepare(int dtype, void* q_out, void* k_cache, void* v_cache, const void* qkv, const float* q_w,
+                             const float* k_w, const float* inv_freq, const int* positions, const int* req_of_token,
+                             const int* block_table, int table_stride, int tokens, int nh, int nkv, int d, int dv, int rot,
+                             int interleaved, int norm_mode, int page_size, int num_pages, float eps, int write_kv, int* err,
+                             cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    const int threads = 128;
+    const size_t smem = ((size_t)rot + (size_t)(threads / 32) * d) * sizeof(float);
+    if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    if (dtype == XB_F32)
+        qkv_prepare_kernel<float><<<tokens, threads, smem, stream>>>(
+            (float*)q_out, (float*)k_cache, (float*)v_cache, (const float*)qkv, q_w, k_w, inv_freq, positions, req_of_token,
+            block_table, table_stride, nh, nkv, d, dv, rot, interleaved, norm_mode, page_size, num_pages, eps, write_kv, err);
+    else
+        qkv_prepare_kernel<__nv_bfloat16><<<tokens, threads, smem, stream>>>(
+            (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (const __nv_bfloat16*)qkv, q_w, k_w,
+            inv_freq, positions, req_of_token, block_table, table_stride, nh, nkv, d, dv, rot, interleaved, norm_mode,
+            page_size, num_pages, eps, write_kv, err);
+    return xb_launch_status();
+}
+
+// ------------------------------------------------------------------------------------------
+// The attention itself on FMA units.  A block takes `bq` consecutive queries of one entry (a query
+// tile) with all heads and walks over the keys in tiles of BK:
+//   1. per kv head: its keys to shared memory, raw scores of the group's query heads;
+//   2. the mix across heads, the causal / window mask;
+//   3. per (head, query) row the running maximum (it starts at 0 with a sink, whose entry is always
+//      there), the weights exp(s - max) and the factor that brings earlier sums to the new maximum;
+//   4. per kv head: its values to shared memory, the value sums of the group's heads (each thread
+//      keeps its share of the tile's outputs in registers).
+// Block x of the grid finds its (entry, tile) by walking over q_start; blocks beyond the last tile
+// leave.  `parts` > 1 (single-token entries with long contexts): the keys of an entry are cut into
+// `parts` ranges, block (x, y) takes range y and leaves its maximum, sum and unnormalised output in
+// scratch; attn_talking_merge_kernel puts the ranges together.
+// ------------------------------------------------------------------------------------------
+constexpr int TA_THREADS = 256;
+constexpr int TA_BK = 32;
+constexpr int TA_OPT = 64;     // most outputs a thread keeps
+
+struct TalkArgs {
+    const int* q_start;
+    const int* start_pos;
+    const int* block_table;
+    const float* talk;
+    float* part_o;     // [tokens, parts, heads, dv]   (parts > 1)
+    float* part_ml;    // [tokens, parts, heads, 2]
+    int num_entries, table_stride, nh, nkv, d, dv, page_size, num_pages, window, sink, bq, parts, ldo;
+    float scale, out_scale;
+    int* err;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(TA_THREADS) attn_talking_kernel(T* __restrict__ out, const T* __restrict__ q,
+                                                                  const T* __restrict__ k_cache, const T* __restrict__ v_cache,
+                                                                  TalkArgs a) {
+    extern __shared__ float sm[];
+    __shared__ int s_entry, s_tile;
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+    const int H = a.nh, G = a.nkv, d = a.d, dv = a.dv, BQ = a.bq, rep = H / G;
+    if (tid == 0) {
+        int tile = blockIdx.x, found = -1;
+        for (int b = 0; b < a.num_entries; ++b) {
+            const int n = a.q_start[b + 1] - a.q_start[b];
+            const int nt = (n + BQ - 1) / BQ;
+            if (tile < nt) { found = b; break; }
+            tile -= nt;
+        }
+        s_entry = found;
+        s_tile = tile;
+    }
+    __syncthreads();
+    const int b = s_entry;
+    if (b < 0) return;
+    const int n_b = a.q_start[b + 1] - a.q_start[b];
+    const int i0 = s_tile * BQ;
+    const int nq = min(BQ, n_b - i0);
+    const int t0 = a.q_start[b] + i0;
+    const int p0 = a.start_pos[b] + i0;           // position of the tile's first query
+    const int* table = a.block_table + (size_t)b * a.table_stride;
+
+    const int ldk = (d > dv ? d : dv) + 1;
+    float* qs = sm;                                   // [BQ][H][d]
+    float* kv = qs + (size_t)BQ * H * d;              // [BK][ldk]
+    float* S = kv + (size_t)TA_BK * ldk;              // [H][BQ][BK] raw
+    float* P = S + (size_t)H * BQ * TA_BK;            // [H][BQ][BK] mixed, then weights
+    float* tk = P + (size_t)H * BQ * TA_BK;           // [H][H]
+    float* rm = tk + (size_t)H * H;                   // [H*BQ] running maximum
+    float* rl = rm + H * BQ;                          // running sum
+    float* rc = rl + H * BQ;                          // this tile's correction factor
+
+    for (int e = tid; e < BQ * H * d; e += TA_THREADS) {
+        const int i = e / (H * d);
+        qs[e] = i < nq ? to_f32<T>(q[(size_t)(t0 + i) * H * d + (e - i * H * d)]) * a.scale : 0.f;
+    }
+    if (a.talk)
+        for (int e = tid; e < H * H; e += TA_THREADS) tk[e] = a.talk[e];
+    for (int e = tid; e < H * BQ; e += TA_THREADS) {
+        rm[e] = a.sink && blockIdx.y == 0 ? 0.f : -INFINITY;
+        rl[e] = a.sink && blockIdx.y == 0 ? 1.f : 0.f;
+    }
+    float o[TA_OPT];
+#pragma unroll
+    for (int k = 0; k < TA_OPT; ++k) o[k] = 0.f;
+    const int n_out = BQ * H * dv;    // element e = (i * H + h) * dv + c
+
+    // the keys this block walks over
+    const int last = p0 + nq - 1;
+    int lo = (a.window > 0 && p0 - a.window + 1 > 0) ? p0 - a.window + 1 : 0;
+    int hi = last + 1;
+    if (a.parts > 1) {
+        const int tiles = (hi - lo / TA_BK * TA_BK + TA_BK - 1) / TA_BK;
+        const int per = (tiles + a.parts - 1) / a.parts;
+        const int first = lo / TA_BK * TA_BK + (int)blockIdx.y * per * TA_BK;
+        lo = max(lo, first);
+        hi = min(hi, first + per * TA_BK);
+    }
+    for (int k0 = lo / TA_BK * TA_BK; k0 < hi; k0 += TA_BK) {
+        // 1. raw scores
+        for (int g = 0; g < G; ++g) {
+            __syncthreads();
+            for (int e = tid; e < TA_BK * d; e += TA_THREADS) {
+                const int j = e / d, c = e - j * d;
+                const int key = k0 + j;
+                float v = 0.f;
+                if (key >= lo && key < hi) {
+                    const int page = table[key / a.page_size];
+                    if (page < 0 || page >= a.num_pages) {
+                        if (c == 0) atomicOr(a.err, XB_ERR_BAD_PAGE);
+                    } else {
+                        v = to_f32<T>(k_cache[(((size_t)page * G + g) * a.page_size + key % a.page_size) * d + c]);
+                    }
+                }
+                kv[j * ldk + c] = v;
+            }
+            __syncthreads();
+            for (int e = tid; e < rep * BQ * TA_BK; e += TA_THREADS) {
+                const int j = e % TA_BK, i = (e / TA_BK) % BQ, h = g * rep + e / (TA_BK * BQ);
+                const float* qr = qs + ((size_t)i * H + h) * d;
+                const float* kr = kv + j * ldk;
+                float s = 0.f;
+                for (int c = 0; c < d; ++c) s = fmaf(qr[c], kr[c], s);
+                S[((size_t)h * BQ + i) * TA_BK + j] = s;
+            }
+        }
+        __syncthreads();
+        // 2. mix and mask
+        for (int e = tid; e < H * BQ * TA_BK; e += TA_THREADS) {
+            const int j = e % TA_BK, i = (e / TA_BK) % BQ, h = e / (TA_BK * BQ);
+            const int key = k0 + j, p = p0 + i;
+            float s;
+            if (a.talk) {
+                s = 0.f;
+                const float* tr = tk + (size_t)h * H;
+                for (int g = 0; g < H; ++g) s = fmaf(tr[g], S[((size_t)g * BQ + i) * TA_BK + j], s);
+            } else {
+                s = S[e];
+            }
+            const bool seen = i < nq && key >= lo && key < hi && key <= p && (a.window <= 0 || key > p - a.window);
+            P[e] = seen ? s : -INFINITY;
+        }
+        __syncthreads();
+        // 3. rows of the softmax
+        for (int r = warp; r < H * BQ; r += TA_THREADS / 32) {
+            float* pr = P + (size_t)r * TA_BK;
+            const float s = pr[lane];
+            const float m_old = rm[r];
+            const float m_new = fmaxf(m_old, warp_max(s));
+            const float w = m_new == -INFINITY ? 0.f : expf(s - m_new);
+            const float sum = warp_sum(w);
+            pr[lane] = w;
+            if (lane == 0) {
+                const float corr = m_new == -INFINITY ? 1.f : expf(m_old - m_new);
+                rc[r] = corr;
+                rl[r] = rl[r] * corr + sum;
+                rm[r] = m_new;
+            }
+        }
+        // 4. value sums
+        for (int g = 0; g < G; ++g) {
+            __syncthreads();
+            for (int e = tid; e < TA_BK * dv; e += TA_THREADS) {
+                const int j = e / dv, c = e - j * dv;
+                const int key = k0 + j;
+                float v = 0.f;
+                if (key >= lo && key < hi) {
+                    const int page = table[key / a.page_size];
+                    if (page >= 0 && page < a.num_pages)
+                        v = to_f32<T>(v_cache[(((size_t)page * G + g) * a.page_size + key % a.page_size) * dv + c]);
+                }
+                kv[j * ldk + c] = v;
+            }
+            __syncthreads();
+#pragma unroll
+            for (int k = 0; k < TA_OPT; ++k) {
+                const int e = tid + k * TA_THREADS;
+                if (e >= n_out) break;
+                const int c = e % dv, ih = e / dv, h = ih % H, i = ih / H;
+                if (h / rep != g) continue;
+                const int r = h * BQ + i;
+                const float* pr = P + (size_t)r * TA_BK;
+                float acc = o[k] * rc[r];
+#pragma unroll 8
+                for (int j = 0; j < TA_BK; ++j) acc = fmaf(pr[j], kv[j * ldk + c], acc);
+                o[k] = acc;
+            }
+        }
+    }
+    __syncthreads();
+    if (a.parts > 1) {
+        // one query per block here (bq == 1): leave this range's maximum, sum and output
+        float* po = a.part_o + ((size_t)t0 * a.parts + blockIdx.y) * H * dv;
+        float* pml = a.part_ml + ((size_t)t0 * a.parts + blockIdx.y) * H * 2;
+#pragma unroll
+        for (int k = 0; k < TA_OPT; ++k) {
+            const int e = tid + k * TA_THREADS;
+            if (e >= n_out) break;
+            po[e] = o[k];
+        }
+        for (int h = tid; h < H; h += TA_THREADS) {
+            pml[2 * h] = rm[h];
+            pml[2 * h + 1] = rl[h];
+        }
+        return;
+    }
+#pragma unroll
+    for (int k = 0; k < TA_OPT; ++k) {
+        const int e = tid + k * TA_THREADS;
+        if (e >= n_out) break;
+        const int c = e % dv, ih = e / dv, h = ih % H, i = ih / H;
+        if (i >= nq) continue;
+        const float l = rl[h * BQ + i];
+        out[(size_t)(t0 + i) * a.ldo + (size_t)h * dv + c] = from_f32<T>(l > 0.f ? o[k] / l * a.out_scale : 0.f);
+    }
+}
+
+// out[t, h] = out_scale * sum_y e^(m_y - m) o_y / sum_y e^(m_y - m) l_y  over the `parts` key ranges of token t
+template <typename T>
+__global__ void attn_talking_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o,
+                                          const float* __restrict__ part_ml, int H, int dv, int parts, int ldo,
+                                          float out_scale) {
+    const int t = blockIdx.x;
+    for (int e = threadIdx.x; e < H * dv; e += blockDim.x) {
+        const int h = e / dv;
+        const float* ml = part_ml + (size_t)t * parts * H * 2 + 2 * h;
+        float m = -INFINITY;
+        for (int y = 0; y < parts; ++y) m = fmaxf(m, ml[(size_t)y * H * 2]);
+        float l = 0.f, acc = 0.f;
+        for (int y = 0; y < parts; ++y) {
+            const float my = ml[(size_t)y * H * 2];
+            if (my == -INFINITY) continue;
+            const float f = expf(my - m);
+            l += f * ml[(size_t)y * H * 2 + 1];
+            acc += f * part_o[((size_t)t * parts + y) * H * dv + e];
+        }
+        out[(size_t)t * ldo + e] = from_f32<T>(l > 0.f ? acc / l * out_scale : 0.f);
+    }
+}
+
+static size_t talking_smem(int H, int d, int dv, int bq) {
+    const int ldk = (d > dv ? d : dv) + 1;
+    return ((size_t)bq * H * d + (size_t)TA_BK * ldk + 2 * (size_t)H * bq * TA_BK + (size_t)H * H + 3 * (size_t)H * bq) * sizeof(float);
+}
+
+// Largest query tile (a power of two up to `want`) whose outputs fit the threads' registers and whose
+// tiles fit shared memory; 0: the sizes do not fit at all.
+XB_EXPORT int xb_attn_talking_tile(int nh, int d, int dv, int want) {
+    for (int bq = 16; bq >= 1; bq >>= 1) {
+        if (bq > want && bq > 1) continue;
+        if ((long long)bq * nh * dv <= (long long)TA_THREADS * TA_OPT && talking_smem(nh, d, dv, bq) <= 200 * 1024) return bq;
+    }
+    return 0;
+}
+
+XB_EXPORT int xb_attn_talking(int dtype, void* out, int ldo, const void* q, const void* k_cache, const void* v_cache,
+                              const float* talk, const int* q_start, const int* start_pos, int num_entries,
+                              const int* block_table, int table_stride, int tokens, int nh, int nkv, int d, int dv,
+                              int page_size, int num_pages, int window, float scale, int sink, float out_scale, int bq,
+                              int parts, float* part_o, float* part_ml, int* err, cudaStream_t stream) {
+    if (tokens <= 0 || num_entries <= 0) return 0;
+    if (bq <= 0 || (long long)bq * nh * dv > (long long)TA_THREADS * TA_OPT || nh % nkv) return (int)cudaErrorInvalidValue;
+    if (parts > 1 && (bq != 1 || !part_o || !part_ml)) return (int)cudaErrorInvalidValue;
+    const size_t smem = talking_smem(nh, d, dv, bq);
+    if (smem > 200 * 1024) return (int)cudaErrorInvalidValue;
+    TalkArgs a;
+    a.q_start = q_start; a.start_pos = start_pos; a.block_table = block_table; a.talk = talk;
+    a.part_o = part_o; a.part_ml = part_ml;
+    a.num_entries = num_entries; a.table_stride = table_stride; a.nh = nh; a.nkv = nkv; a.d = d; a.dv = dv;
+    a.page_size = page_size; a.num_pages = num_pages; a.window = window; a.sink = sink; a.bq = bq;
+    a.parts = parts < 1 ? 1 : parts; a.ldo = ldo; a.scale = scale; a.out_scale = out_scale; a.err = err;
+    const dim3 grid((tokens + bq - 1) / bq + num_entries, a.parts);
+    int rc;
+    if (dtype == XB_F32) {
+        cudaFuncSetAttribute(attn_talking_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attn_talking_kernel<float><<<grid, TA_THREADS, smem, stream>>>((float*)out, (const float*)q, (const float*)k_cache,
+                                                                      (const float*)v_cache, a);
+        rc = xb_launch_status();
+        if (rc == 0 && a.parts > 1) {
+            attn_talking_merge_kernel<float><<<tokens, 128, 0, stream>>>((float*)out, part_o, part_ml, nh, dv, a.parts, ldo, out_scale);
+            rc = xb_launch_status();
+        }
+    } else {
+        typedef __nv_bfloat16 bf;
+        cudaFuncSetAttribute(attn_talking_kernel<bf>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attn_talking_kernel<bf><<<grid, TA_THREADS, smem, stream>>>((bf*)out, (const bf*)q, (const bf*)k_cache,
+                                                                   (const bf*)v_cache, a);
+        rc = xb_launch_status();
+        if (rc == 0 && a.parts > 1) {
+            attn_talking_merge_kernel<bf><<<tokens, 128, 0, stream>>>((bf*)out, part_o, part_ml, nh, dv, a.parts, ldo, out_scale);
+            rc = xb_launch_status();
+        }
+    }
+    return rc;
+}

@@ -132,7 +132,8 @@ def embedding(out, table, ids, err, sampled=None, scale=None):
     """out[t] = table[ids[t]] (times ``scale``, if given, rounded to the table's dtype); an id -1 - i
     is replaced on the device by ``sampled[i]`` (int32 ids a sampler left there)."""
     T, H = out.shape
-    _need(out, "out", table.dtype, (T, H))
+    wide = out.dtype == torch.float32 and table.dtype != torch.float32     # a float32 stream over a bfloat16 table
+    _need(out, "out", torch.float32 if wide else table.dtype, (T, H))
     _need(table, "table", None, (None, H))
     _need(ids, "ids", torch.int32)
     if ids.numel() < T:
@@ -140,6 +141,11 @@ def embedding(out, table, ids, err, sampled=None, scale=None):
     _need(err, "err", torch.int32)
     if sampled is not None:
         _need(sampled, "sampled", torch.int32)
+    if wide:
+        _ok(kernels_lib().xb_embedding_f32(dtype_code(table.dtype), out.data_ptr(), table.data_ptr(), ids.data_ptr(),
+                                           _ptr(sampled), sampled.numel() if sampled is not None else 0, T, H, table.shape[0],
+                                           1.0 if scale is None else float(scale), err.data_ptr(), _stream()), "embedding_f32")
+        return
     _ok(kernels_lib().xb_embedding(dtype_code(table.dtype), out.data_ptr(), table.data_ptr(), ids.data_ptr(),
                                    _ptr(sampled), sampled.numel() if sampled is not None else 0,
                                    T, H, table.shape[0], 1.0 if scale is None else float(scale), err.data_ptr(),
@@ -159,8 +165,26 @@ def rmsnorm(out, x, weight, eps, err, *, branch=None, sum_out=None, rows=None, w
     dim = x.shape[-1]
     n = out.shape[0]
     _need(x, "x", None, (None, dim))
-    _need(out, "out", x.dtype, (n, dim))
     _need(weight, "weight", torch.float32, (dim,))
+    if x.dtype == torch.float32 and (out.dtype != torch.float32 or (branch is not None and branch.dtype != torch.float32)):
+        # a float32 stream beside activations in the engine's type
+        _need(out, "out", None, (n, dim))
+        if branch is not None:
+            _need(branch, "branch", None, tuple(x.shape))
+        if sum_out is not None:
+            _need(sum_out, "sum_out", torch.float32, (n, dim))
+        if rows is not None:
+            _need(rows, "rows", torch.int32)
+            if rows.numel() < n:
+                raise KernelError(f"rows holds {rows.numel()} entries for {n} output rows")
+        elif n != x.shape[0]:
+            raise KernelError(f"out has {n} rows, x has {x.shape[0]} and no row list was given")
+        _ok(kernels_lib().xb_rmsnorm_f32(dtype_code(branch.dtype) if branch is not None else F32, dtype_code(out.dtype),
+                                         out.data_ptr(), _ptr(sum_out), x.data_ptr(), _ptr(branch), _ptr(rows),
+                                         weight.data_ptr(), n, dim, x.shape[0], float(eps), float(weight_offset),
+                                         err.data_ptr(), _stream()), "rmsnorm_f32")
+        return
+    _need(out, "out", x.dtype, (n, dim))
     if branch is not None:
         _need(branch, "branch", x.dtype, tuple(x.shape))
     if sum_out is not None:
@@ -183,6 +207,12 @@ def rmsnorm(out, x, weight, eps, err, *, branch=None, sum_out=None, rows=None, w
 
 def add(out, x, branch):
     _need(x, "x")
+    if x.dtype == torch.float32 and branch.dtype != torch.float32:
+        _need(branch, "branch", None, tuple(x.shape))
+        _need(out, "out", torch.float32, tuple(x.shape))
+        _ok(kernels_lib().xb_add_f32(dtype_code(branch.dtype), out.data_ptr(), x.data_ptr(), branch.data_ptr(), x.numel(),
+                                     _stream()), "add_f32")
+        return
     _need(branch, "branch", x.dtype, tuple(x.shape))
     _need(out, "out", x.dtype, tuple(x.shape))
     _ok(kernels_lib().xb_add(dtype_code(x.dtype), out.data_ptr(), x.data_ptr(), branch.data_ptr(), x.numel(), _stream()), "add")
@@ -574,3 +604,135 @@ def attn_prefill_tc(out, q, k_cache, v_cache, q_start, start_pos, block_table, t
         return False
     _ok(rc, "attn_prefill_tc")
     return True
+
+
+# ---- attention with talking heads and a sink; gated recurrence; polynomial activation; table experts ----
+def qkv_prepare(q_out, k_cache, v_cache, qkv, q_w, k_w, inv_freq, positions, req_of_token, block_table, table_stride,
+                nh, nkv, d, dv, rot, interleaved, norm_mode, eps, write_kv, err):
+    """Per q/k head of the packed ``qkv`` rows ``[heads*d | kv_heads*d | kv_heads*dv]``: norm over the head
+    (``norm_mode`` 1: before the rotation, 2: after it, 0: none; weight ``q_w`` / ``k_w`` or none), rotation of
+    the first ``rot`` channels by ``position * inv_freq`` (float32 angles formed in the kernel; ``inv_freq`` None:
+    no rotation); q to ``q_out``, k and v into their pages."""
+    T = qkv.shape[0]
+    _need(qkv, "qkv", None, (T, (nh + nkv) * d + nkv * dv))
+    _need(q_out, "q_out", qkv.dtype, (T, nh, d))
+    if write_kv:
+        _need(k_cache, "k_cache", qkv.dtype, (None, nkv, None, d))
+        _need(v_cache, "v_cache", qkv.dtype, (k_cache.shape[0], nkv, k_cache.shape[2], dv))
+    num_pages = k_cache.shape[0] if k_cache is not None else 0
+    page_size = k_cache.shape[2] if k_cache is not None else 1
+    for name, w_ in (("q_norm", q_w), ("k_norm", k_w)):
+        if w_ is not None:
+            _need(w_, name, torch.float32, (d,))
+    if inv_freq is not None:
+        _need(inv_freq, "inv_freq", torch.float32, (rot // 2,))
+    _ok(kernels_lib().xb_qkv_prepare(
+        dtype_code(qkv.dtype), q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache), qkv.data_ptr(), _ptr(q_w), _ptr(k_w),
+        _ptr(inv_freq), positions.data_ptr(), req_of_token.data_ptr(), block_table.data_ptr(), int(table_stride), T, nh, nkv,
+        d, dv, int(rot if inv_freq is not None else 0), int(bool(interleaved)), int(norm_mode), page_size, num_pages,
+        float(eps), int(bool(write_kv)), err.data_ptr(), _stream()), "qkv_prepare")
+
+
+def attn_talking_tile(nh: int, d: int, dv: int, want: int) -> int:
+    """The query tile ``attn_talking`` can take for these sizes (a power of two, at most ``want``
+    unless that is below one); 0: the sizes do not fit the kernel."""
+    return int(kernels_lib().xb_attn_talking_tile(int(nh), int(d), int(dv), int(max(want, 1))))
+
+
+def attn_talking(out, q, k_cache, v_cache, talk, q_start, start_pos, num_entries, block_table, table_stride, window, scale,
+                 sink, out_scale, bq, err, parts: int = 1, part_o=None, part_ml=None):
+    """Attention over the paged cache with scores mixed across heads by ``talk`` ([heads, heads] float32 or
+    None) before the softmax and, with ``sink``, one silent entry of score 0 in every softmax.  ``out`` is a
+    view ``[T, heads * dv]`` whose rows may be ``out.stride(0)`` apart; it receives ``out_scale`` times the
+    result.  ``bq``: queries per block (``attn_talking_tile``).  ``parts`` > 1 (only with ``bq`` 1): every
+    token's keys are cut into that many ranges, merged through ``part_o`` / ``part_ml`` (float32,
+    T*parts*heads*dv and T*parts*heads*2 elements)."""
+    T, nh, d = q.shape
+    _need(q, "q", None, (T, nh, d))
+    _need(k_cache, "k_cache", q.dtype, (None, None, None, d))
+    num_pages, nkv, ps, _ = k_cache.shape
+    dv = v_cache.shape[-1]
+    _need(v_cache, "v_cache", q.dtype, (num_pages, nkv, ps, dv))
+    if out.dtype != q.dtype or out.shape != (T, nh * dv) or out.stride(1) != 1 or not out.is_cuda:
+        raise KernelError(f"out must be a {q.dtype} view [T, heads * dv] with unit column stride")
+    if talk is not None:
+        _need(talk, "talk", torch.float32, (nh, nh))
+    if parts > 1:
+        _need(part_o, "part_o", torch.float32)
+        _need(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < T * parts * nh * dv or part_ml.numel() < T * parts * nh * 2:
+            raise KernelError("attention scratch buffers are too small for the number of key ranges")
+    _ok(kernels_lib().xb_attn_talking(
+        dtype_code(q.dtype), out.data_ptr(), int(out.stride(0)), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+        _ptr(talk), q_start.data_ptr(), start_pos.data_ptr(), int(num_entries), block_table.data_ptr(), int(table_stride),
+        T, nh, nkv, d, dv, ps, num_pages, int(window or 0), float(scale), int(bool(sink)), float(out_scale), int(bq),
+        int(parts), _ptr(part_o), _ptr(part_ml), err.data_ptr(), _stream()), "attn_talking", 2 if parts > 1 else 1)
+
+
+def gated_scan(y, zxg, bz, bx, state, q_start, slots, req_of_token, num_entries, out_scale, scratch=None):
+    """The minGRU recurrence over a step's tokens: ``zxg`` float32 ``[T, 3 * width]`` (the z, x and g
+    projections without biases), ``state`` float32 ``[slots, width]`` carried per request, ``y`` a view
+    ``[T, width]`` (rows ``y.stride(0)`` apart) that receives ``out_scale * S * silu(g)``.  With
+    ``scratch`` (float32, 3 * T * width) the chunked form runs."""
+    T, W3 = zxg.shape
+    W = W3 // 3
+    _need(zxg, "zxg", torch.float32, (T, 3 * W))
+    _need(bz, "bz", torch.float32, (W,))
+    _need(bx, "bx", torch.float32, (W,))
+    _need(state, "state", torch.float32, (None, W))
+    if y.shape != (T, W) or y.stride(1) != 1 or not y.is_cuda:
+        raise KernelError("y must be a view [T, width] with unit column stride")
+    if scratch is not None:
+        _need(scratch, "scratch", torch.float32)
+        if scratch.numel() < 3 * T * W:
+            raise KernelError("the scan's scratch is smaller than 3 * tokens * width")
+    _ok(kernels_lib().xb_gated_scan(dtype_code(y.dtype), y.data_ptr(), int(y.stride(0)), zxg.data_ptr(), bz.data_ptr(),
+                                    bx.data_ptr(), state.data_ptr(), q_start.data_ptr(), slots.data_ptr(),
+                                    req_of_token.data_ptr(), int(num_entries), T, W, float(out_scale),
+                                    int(scratch is not None), _ptr(scratch), _stream()), "gated_scan",
+        3 if scratch is not None else 1)
+
+
+def polynorm(out, z, coef, eps):
+    """out = a N(z) + b N(z^2) + c N(z^3) + e per row, N dividing by the root mean square; float32 ``z``."""
+    T, Fdim = z.shape
+    _need(z, "z", torch.float32, (T, Fdim))
+    _need(out, "out", None, (T, Fdim))
+    _need(coef, "coef", torch.float32, (4,))
+    _ok(kernels_lib().xb_polynorm(dtype_code(out.dtype), out.data_ptr(), z.data_ptr(), coef.data_ptr(), T, Fdim, float(eps),
+                                  _stream()), "polynorm")
+
+
+def expert_route(offsets, perm, inv, table, ids, sampled, req_of_token, tokens, top, experts, err):
+    _need(table, "table", torch.int32, (None, top))
+    for name, t_, n in (("offsets", offsets, experts + 1), ("perm", perm, tokens * top), ("inv", inv, tokens * top)):
+        _need(t_, name, torch.int32)
+        if t_.numel() < n:
+            raise KernelError(f"{name} holds {t_.numel()} entries, {n} are needed")
+    _ok(kernels_lib().xb_expert_route(offsets.data_ptr(), perm.data_ptr(), inv.data_ptr(), table.data_ptr(), ids.data_ptr(),
+                                      _ptr(sampled), sampled.numel() if sampled is not None else 0, req_of_token.data_ptr(),
+                                      int(tokens), int(top), int(experts), table.shape[0], err.data_ptr(), _stream()),
+        "expert_route")
+
+
+def expert_gemm(y, a, w, offsets, perm, gather: bool, top: int, gated: bool):
+    """y[r] = a[src(r)] . w[e(r)]^T over rows grouped by expert (``expert_route``); ``w`` is
+    ``[experts, N, K]`` (``[experts, 2 N, K]`` when ``gated``: y = silu(gate) * up)."""
+    E = w.shape[0]
+    N = w.shape[1] // (2 if gated else 1)
+    K = w.shape[2]
+    rows = y.shape[0]
+    _need(w, "w", a.dtype, (E, None, K))
+    _need(a, "a", None, (None, K))
+    _need(y, "y", None, (rows, N))
+    _ok(kernels_lib().xb_expert_gemm(dtype_code(a.dtype), dtype_code(y.dtype), y.data_ptr(), a.data_ptr(), w.data_ptr(),
+                                     offsets.data_ptr(), perm.data_ptr(), int(bool(gather)), int(top), E, rows, N, K,
+                                     int(bool(gated)), _stream()), "expert_gemm")
+
+
+def expert_combine(out, y, inv, top: int):
+    T, N = out.shape
+    _need(y, "y", torch.float32, (None, N))
+    _need(out, "out", None, (T, N))
+    _ok(kernels_lib().xb_expert_combine(dtype_code(out.dtype), out.data_ptr(), y.data_ptr(), inv.data_ptr(), T, int(top), N,
+                                        _stream()), "expert_combine")

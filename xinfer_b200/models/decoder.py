@@ -42,6 +42,8 @@ class DecoderModel:
         self.device = torch.device(device)
         self.blocks = [Block(b, dtype, self.device) for b in plan.blocks]
         self.final_norm = build_part("norm", plan.final_norm, plan.final_norm_name, dtype, self.device)
+        # the residual stream's dtype: the engine's, or float32 where the plan says so
+        self.stream_dtype = torch.float32 if plan.residual_dtype == "float32" else dtype
         self.embed = None
         self.head = None
 
@@ -94,7 +96,8 @@ class DecoderModel:
         ``[num_logit_rows, vocab]`` for ``ctx.logit_rows``."""
         T, H, V = ctx.num_tokens, self.plan.hidden, self.plan.vocab_size
         ws = ctx.workspace
-        x = ws.get("model.x", (T, H), self.dtype)
+        x = ws.get("model.x", (T, H), self.stream_dtype)
+        ctx.branch_dtype = self.stream_dtype
         # what mixers decide once per step from its metadata, before the step's first kernel
         for pos, run in enumerate(self.plan.runs):
             mixer = self.blocks[run.block].mixer

@@ -114,4 +114,15 @@ def _declare_kernels(lib):
          [P, P, P, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, F, I, I, I, I, I, P, P, P])
     _sig(lib, "xb_attn_decode_plan_size", c_longlong, [I, I, I])
     _sig(lib, "xb_attn_decode_plan", I, [P, P, P, P, I, I, I, I, I, I, I, I, P, P])
+    _sig(lib, "xb_embedding_f32", I, [I, P, P, P, P, I, I, I, I, F, P, P])
+    _sig(lib, "xb_rmsnorm_f32", I, [I, I, P, P, P, P, P, P, I, I, I, F, F, P, P])
+    _sig(lib, "xb_add_f32", I, [I, P, P, P, L, P])
+    _sig(lib, "xb_qkv_prepare", I, [I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P])
+    _sig(lib, "xb_attn_talking_tile", I, [I, I, I, I])
+    _sig(lib, "xb_attn_talking", I, [I, P, I, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, I, F, I, I, P, P, P, P])
+    _sig(lib, "xb_gated_scan", I, [I, P, I, P, P, P, P, P, P, P, I, I, I, F, I, P, P])
+    _sig(lib, "xb_polynorm", I, [I, P, P, P, I, I, F, P])
+    _sig(lib, "xb_expert_route", I, [P, P, P, P, P, P, I, P, I, I, I, I, P, P])
+    _sig(lib, "xb_expert_gemm", I, [I, I, P, P, P, P, P, I, I, I, I, I, I, I, P])
+    _sig(lib, "xb_expert_combine", I, [I, P, P, P, I, I, I, P])
     _sig(lib, "xb_attn_decode_tc", I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, I, P, I, P, P])

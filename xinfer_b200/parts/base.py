@@ -95,6 +95,9 @@ class StepContext:
     sampled: Optional[torch.Tensor] = None
     # values parts compute once per step and share between layers
     scratch: Dict[str, Any] = field(default_factory=dict)
+    # the type in which a mixer or feed-forward that can choose hands its result to the residual stream
+    # (float32 where the model keeps a float32 stream); None: the engine's dtype
+    branch_dtype: Optional[torch.dtype] = None
 
 
 @dataclass(frozen=True)
@@ -206,6 +209,24 @@ class Mixer(Part):
 
     def forward(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache],
                 state: Optional[Dict[str, torch.Tensor]], writes_cache: bool = True) -> torch.Tensor:
+        raise NotImplementedError
+
+    # A mixer whose last operation is a projection ``inner . W_o^T`` may offer its two halves, so that a mixer
+    # that combines several mixers runs ONE projection over their concatenated inner activations (the sum of
+    # the branches then forms in the product's float32 accumulators).
+    def inner_width(self) -> Optional[int]:
+        """Width of the activation that enters the output projection; None: not offered."""
+        return None
+
+    def forward_inner(self, x: torch.Tensor, ctx: StepContext, cache: Optional[LayerCache],
+                      state: Optional[Dict[str, torch.Tensor]], writes_cache: bool, out: torch.Tensor,
+                      out_scale: float) -> None:
+        """Everything before the output projection: ``out`` (a view ``[T, inner_width]`` whose rows may be
+        further apart than their width) receives ``out_scale`` times the inner activation."""
+        raise NotImplementedError
+
+    def output_weight(self) -> torch.Tensor:
+        """``W_o`` ``[hidden, inner_width]`` in the engine's dtype."""
         raise NotImplementedError
 
 

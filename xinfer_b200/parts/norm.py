@@ -23,11 +23,11 @@ class RMSNorm(Norm):
 
     @classmethod
     def weight_specs(cls, spec: NormSpec, prefix: str) -> List[WeightSpec]:
-        return [WeightSpec(prefix + "weight", (spec.dim,), "norm")]
+        return [WeightSpec(prefix + spec.weight_name, (spec.dim,), spec.init)]
 
     def load(self, store) -> None:
         # norm weights are held in float32 whatever the activations are (src/models/qwen3.rs:83)
-        self.weight = store.get(self.prefix + "weight", self.device, torch.float32).float().contiguous()
+        self.weight = store.get(self.prefix + self.spec.weight_name, self.device, torch.float32).float().contiguous()
 
     def forward(self, out, x, ctx, branch=None, sum_out=None, rows=None):
         kernels.rmsnorm(out, x, self.weight, self.spec.eps, ctx.err, branch=branch, sum_out=sum_out,

@@ -26,9 +26,22 @@ class RotaryTables:
 _TABLE_CACHE = {}
 
 
-def inv_frequencies(theta: float, rotary_dim: int) -> np.ndarray:
+def inv_frequencies(theta: float, rotary_dim: int, scaling=None, rounded_once: bool = False) -> np.ndarray:
+    """``rounded_once``: formed in float64 and rounded to float32 at the end (the table path without scaling
+    keeps the reference's order: the power rounded to float32, then its reciprocal)."""
     j = np.arange(0, rotary_dim, 2, dtype=np.float64)
-    return (np.float32(1.0) / np.power(np.float64(theta), j / np.float64(rotary_dim)).astype(np.float32)).astype(np.float32)
+    if scaling is None and not rounded_once:
+        return (np.float32(1.0) / np.power(np.float64(theta), j / np.float64(rotary_dim)).astype(np.float32)).astype(np.float32)
+    # long wavelengths turn more slowly (``RopeScaling``); formed in float64, rounded once to float32
+    f = np.power(np.float64(theta), -j / np.float64(rotary_dim))
+    if scaling is None:
+        return f.astype(np.float32)
+    wavelength = 2.0 * np.pi / f
+    s = (scaling.original / wavelength - scaling.low) / (scaling.high - scaling.low)
+    blended = (1.0 - s) * f / scaling.factor + s * f
+    f = np.where(wavelength < scaling.original / scaling.high, f,
+                 np.where(wavelength > scaling.original / scaling.low, f / scaling.factor, blended))
+    return f.astype(np.float32)
 
 
 class Rope(PositionEncoding):
@@ -42,14 +55,28 @@ class Rope(PositionEncoding):
         if spec.layout not in ("neox", "interleaved"):
             raise ValueError(f"unknown rotary layout '{spec.layout}'")
         self._tables = None
+        self._inv = None
+
+    def frequencies(self) -> torch.Tensor:
+        """float32 ``[rotary_dim / 2]`` on the device: what a kernel that forms its angles itself multiplies
+        a position by."""
+        if self._inv is None:
+            s = self.spec
+            key = ("inv", str(self.device), s.theta, s.rotary_dim, s.scaling)
+            if key not in _TABLE_CACHE:
+                _TABLE_CACHE[key] = torch.from_numpy(inv_frequencies(s.theta, s.rotary_dim, s.scaling, True)).to(self.device)
+            self._inv = _TABLE_CACHE[key]
+        return self._inv
 
     def rotary(self) -> RotaryTables:
+        if not self.spec.tables:
+            raise ValueError("this rotary encoding keeps no tables (its spec says tables=False); use frequencies()")
         if self._tables is None:
             s = self.spec
-            key = (str(self.device), s.theta, s.rotary_dim, s.max_positions)
+            key = (str(self.device), s.theta, s.rotary_dim, s.max_positions, s.scaling)
             if key not in _TABLE_CACHE:  # layers with the same constants share one table
                 half = s.rotary_dim // 2
-                inv = torch.from_numpy(inv_frequencies(s.theta, s.rotary_dim)).to(self.device)
+                inv = torch.from_numpy(inv_frequencies(s.theta, s.rotary_dim, s.scaling)).to(self.device)
                 cos = torch.empty((s.max_positions, half), dtype=torch.float32, device=self.device)
                 sin = torch.empty_like(cos)
                 kernels.rope_table(cos, sin, inv)

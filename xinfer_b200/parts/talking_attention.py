@@ -1,0 +1,130 @@
+"""Grouped-query attention whose heads talk to each other before the softmax.
+
+    q = W_q h, k = W_k h, v = W_v h         heads of size head_dim (q, k) and v_head_dim (v)
+    q, k: per-head norm (with or without a learned weight) before or after the rotary encoding
+    raw_g[i, j] = scale * q_g[i] . k_kv(g)[j]
+    s_h[i, j]   = sum_g talk[h, g] raw_g[i, j]                          (``talking_heads``)
+    p_h[i, j]   = exp(s_h[i, j]) / (sink + sum_j' exp(s_h[i, j']))      sink = 1 (``sink``) or 0
+    out         = W_o concat_h( sum_j p_h[i, j] v_kv(h)[j] )
+
+Causal, optionally within a window; query head h reads key/value head h // (heads / kv_heads).  With a
+sink the weights of a row sum to less than one: a query may attend to nothing.  Keys after rotation and
+norm, and values, live in the paged cache; scores, mix, softmax and value sums are float32.
+"""
+from __future__ import annotations
+
+from typing import List
+
+import torch
+
+from .. import kernels
+from ..config.plan import AttentionSpec
+from ..weights.loader import WeightSpec
+from .base import CacheTensor, LayerCache, Mixer, PagedCacheNeed, StepContext, build_part, register_mixer
+from .linear import linear
+
+_DEFAULT_NAMES = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "talk.weight")
+# a single-token step cuts every token's keys into ranges so that about this many blocks run
+_DECODE_BLOCKS = 296
+_DECODE_MIN_KEYS = 128
+
+
+class TalkingAttention(Mixer):
+    kind = "talking_attention"
+    graph_safe = True
+
+    def __init__(self, spec: AttentionSpec, prefix: str, dtype, device):
+        super().__init__(spec, prefix, dtype, device)
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError(f"{spec.num_heads} heads do not divide into {spec.num_kv_heads} key/value heads")
+        self.position = build_part("position", spec.rope, prefix, dtype, device) if spec.rope is not None else None
+        if self.position is not None and not hasattr(self.position, "frequencies"):
+            raise ValueError("this attention needs a rotary position encoding that offers its frequencies")
+        self.names = tuple(spec.names) if spec.names else _DEFAULT_NAMES
+        self.w_qkv = self.w_o = self.talk = self.q_norm = self.k_norm = None
+
+    @classmethod
+    def weight_specs(cls, spec: AttentionSpec, prefix: str) -> List[WeightSpec]:
+        n = tuple(spec.names) if spec.names else _DEFAULT_NAMES
+        d, dv = spec.head_dim, spec.value_dim
+        out = [
+            WeightSpec(prefix + n[0], (spec.num_heads * d, spec.hidden)),
+            WeightSpec(prefix + n[1], (spec.num_kv_heads * d, spec.hidden)),
+            WeightSpec(prefix + n[2], (spec.num_kv_heads * dv, spec.hidden)),
+            WeightSpec(prefix + n[3], (spec.hidden, spec.num_heads * dv)),
+        ]
+        if spec.talking_heads:
+            out.append(WeightSpec(prefix + n[4], (spec.num_heads, spec.num_heads), "unit"))
+        if spec.qk_norm and spec.qk_norm_weight:
+            out += [WeightSpec(prefix + "q_norm.weight", (d,), "norm"), WeightSpec(prefix + "k_norm.weight", (d,), "norm")]
+        return out
+
+    def load(self, store) -> None:
+        p, n, s = self.prefix, self.names, self.spec
+        parts = [store.get(p + n[i], self.device, self.dtype, operand=True) for i in range(3)]
+        self.w_qkv = torch.cat(parts, dim=0).contiguous()
+        del parts
+        self.w_o = store.get(p + n[3], self.device, self.dtype, operand=True)
+        if s.talking_heads:
+            self.talk = store.get(p + n[4], self.device, torch.float32).float().contiguous()
+        if s.qk_norm and s.qk_norm_weight:
+            self.q_norm = store.get(p + "q_norm.weight", self.device, torch.float32).float().contiguous()
+            self.k_norm = store.get(p + "k_norm.weight", self.device, torch.float32).float().contiguous()
+
+    def cache_need(self) -> PagedCacheNeed:
+        s = self.spec
+        return PagedCacheNeed((("k", CacheTensor((s.num_kv_heads, s.head_dim), None, 1)),
+                               ("v", CacheTensor((s.num_kv_heads, s.value_dim), None, 1))), s.window)
+
+    # ---- the two halves ---------------------------------------------------------------------------
+    def inner_width(self) -> int:
+        return self.spec.num_heads * self.spec.value_dim
+
+    def output_weight(self) -> torch.Tensor:
+        return self.w_o
+
+    def forward_inner(self, x, ctx: StepContext, cache: LayerCache, state, writes_cache, out, out_scale) -> None:
+        s = self.spec
+        T = x.shape[0]
+        nh, nkv, d, dv = s.num_heads, s.num_kv_heads, s.head_dim, s.value_dim
+        ws = ctx.workspace
+        qkv = ws.get("tattn.qkv", (T, (nh + nkv) * d + nkv * dv), self.dtype)
+        linear(qkv, x, self.w_qkv, ctx.err)
+        q = ws.get("tattn.q", (T, nh, d), self.dtype)
+        table, stride = ctx.tables[cache.group], ctx.strides[cache.group]
+        rope = self.position.spec if self.position is not None else None
+        norm_mode = 0 if not s.qk_norm else (2 if s.qk_norm_after_rope else 1)
+        kernels.qkv_prepare(q, cache["k"], cache["v"], qkv, self.q_norm, self.k_norm,
+                            self.position.frequencies() if rope is not None else None, ctx.positions, ctx.req_of_token,
+                            table, stride, nh, nkv, d, dv, rope.rotary_dim if rope is not None else 0,
+                            rope is not None and rope.layout == "interleaved", norm_mode, s.qk_norm_eps, writes_cache,
+                            ctx.err)
+        # queries per block: the longest portion decides (a step of single tokens takes one query per block
+        # and cuts the keys instead); a replayed step must not look at its actual lengths
+        single = ctx.all_single or ctx.fixed_shapes
+        longest = 1 if single else int((ctx.h_q_start[1:] - ctx.h_q_start[:-1]).max())
+        bq = kernels.attn_talking_tile(nh, d, dv, longest)
+        if bq <= 0:
+            raise kernels.KernelError(f"attention with {nh} heads of {d}/{dv} channels does not fit the kernel's tile")
+        parts, part_o, part_ml = 1, None, None
+        if single and bq == 1:
+            bound = stride * cache.page_size if ctx.fixed_shapes else ctx.max_context
+            if s.window:
+                bound = min(bound, s.window + 32)
+            parts = max(1, min(_DECODE_BLOCKS // max(T, 1), bound // _DECODE_MIN_KEYS, 64))
+            if parts > 1:
+                part_o = ws.get("tattn.part_o", (T * parts * nh * dv,), torch.float32)
+                part_ml = ws.get("tattn.part_ml", (T * parts * nh * 2,), torch.float32)
+        kernels.attn_talking(out, q, cache["k"], cache["v"], self.talk, ctx.q_start, ctx.start_pos, ctx.num_entries, table,
+                             stride, s.window, s.scale, s.sink, out_scale, bq, ctx.err, parts, part_o, part_ml)
+
+    def forward(self, x, ctx: StepContext, cache: LayerCache, state=None, writes_cache: bool = True):
+        T = x.shape[0]
+        inner = ctx.workspace.get("tattn.inner", (T, self.inner_width()), self.dtype)
+        self.forward_inner(x, ctx, cache, state, writes_cache, inner, 1.0)
+        out = ctx.workspace.get("tattn.out", (T, self.spec.hidden), ctx.branch_dtype or self.dtype)
+        linear(out, inner, self.w_o, ctx.err)
+        return out
+
+
+register_mixer("talking_attention", TalkingAttention)

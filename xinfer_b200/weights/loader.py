@@ -60,8 +60,10 @@ class WeightSpec:
     name: str
     shape: Tuple[int, ...]
     # how the random-weights mode draws it: "linear", "embedding" (both N(0, std)),
-    # "norm" (1 + N(0, norm_std)), "zeros", "ones"
+    # "norm" (1 + N(0, norm_std)), "around_zero" (N(0, norm_std)), "unit" (N(0, 1)), "zeros", "ones",
+    # "choice" (int32: every row holds distinct numbers below ``param``)
     init: str = "linear"
+    param: int = 0
 
 
 _FLOATS = (torch.float16, torch.bfloat16, torch.float32, torch.float64)

@@ -35,6 +35,16 @@ def draw(spec: WeightSpec, seed: int, std: float, norm_std: float, dtype: torch.
         t = torch.randn(shape, generator=g, dtype=torch.float32, device=device).mul_(std)
     elif spec.init == "norm":
         t = torch.randn(shape, generator=g, dtype=torch.float32, device=device).mul_(norm_std).add_(1.0)
+    elif spec.init == "around_zero":
+        t = torch.randn(shape, generator=g, dtype=torch.float32, device=device).mul_(norm_std)
+    elif spec.init == "unit":
+        t = torch.randn(shape, generator=g, dtype=torch.float32, device=device)
+    elif spec.init == "choice":
+        if len(shape) != 2 or not (0 < shape[1] <= spec.param):
+            raise ValueError(f"weight '{spec.name}': a choice table needs rows of at most {spec.param} entries")
+        # the first entries of a random order of 0..param-1 per row: distinct within a row
+        keys = torch.rand((shape[0], int(spec.param)), generator=g, dtype=torch.float32, device=device)
+        return keys.argsort(dim=1)[:, : shape[1]].to(torch.int32).contiguous()
     elif spec.init == "zeros":
         t = torch.zeros(shape, dtype=torch.float32, device=device)
     elif spec.init == "ones":
@@ -62,16 +72,19 @@ def write_random_model(model_dir: str, config_dict: Mapping[str, Any], seed: int
     os.makedirs(model_dir, exist_ok=True)
     by_name = {s.name: s for s in specs}
 
+    def stored(spec: WeightSpec) -> torch.dtype:
+        return torch.int32 if spec.init == "choice" else dtype
+
     def produce(name: str) -> torch.Tensor:
         t = draw(by_name[name], seed, std, norm_std, dtype)
         if override is not None:
             t2 = override(name, t)
             if t2 is not None:
-                t = t2.to(dtype)
+                t = t2.to(stored(by_name[name]))
         return t
 
     write_safetensors(os.path.join(model_dir, "model.safetensors"),
-                      [(s.name, tuple(s.shape), dtype) for s in specs], produce,
+                      [(s.name, tuple(s.shape), stored(s)) for s in specs], produce,
                       metadata={"format": "pt", "seed": str(int(seed))})
     with open(os.path.join(model_dir, "config.json"), "w", encoding="utf-8") as f:
         json.dump(dict(config_dict), f, indent=1)
