@@ -66,7 +66,8 @@ def run_trace(model_dir: str, dtype: str, steps: List[dict], out_dir: str, max_t
               page_size: int = 16, max_num_seqs: int = 8, timeout: int = 600) -> Dict[int, np.ndarray]:
     """Run bin/trace_run on the steps and return {step: logits [wanted, vocab]}."""
     with open(os.path.join(model_dir, "config.json")) as f:
-        vocab = json.load(f)["vocab_size"]
+        raw = json.load(f)
+        vocab = raw["vocab_size"] if "vocab_size" in raw else raw["vocab"]
     text = "".join(json.dumps(s) + "\n" for s in steps)
     cmd = [sys.executable, os.path.join(ROOT, "bin", "trace_run"), "--model", model_dir, "--dtype", dtype,
            "--out", out_dir, "--max-tokens", str(max_tokens), "--page-size", str(page_size),

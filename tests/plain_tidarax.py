@@ -11,6 +11,16 @@ from typing import Dict, List, Optional
 import torch
 
 
+# Where an engine that computes its matrix products in bfloat16 stores activations in that type, ``forward``
+# with ``round_to=torch.bfloat16`` rounds them too: the difference to the unrounded run is the drift that
+# rounding alone causes, which the tests take as their yardstick.
+_ROUND = None
+
+
+def _r(x: torch.Tensor) -> torch.Tensor:
+    return x if _ROUND is None else x.to(_ROUND).to(x.dtype)
+
+
 def unit_rms(x: torch.Tensor, eps: float) -> torch.Tensor:
     """x over its root mean square along the last axis, eps under the root."""
     return x / torch.sqrt((x * x).mean(dim=-1, keepdim=True) + eps)
@@ -78,12 +88,12 @@ def talking_sink_attention(q, k, v, talk, scale: float) -> torch.Tensor:
 def attention_branch(h, positions, w: Dict[str, torch.Tensor], p: str, c: dict, eps: float) -> torch.Tensor:
     n = h.shape[0]
     H, G, d, dv = c["heads"], c["kv_heads"], c["dim"], c["vdim"]
-    q = (h @ w[p + "q"].T).view(n, H, d)
-    k = (h @ w[p + "k"].T).view(n, G, d)
-    v = (h @ w[p + "v"].T).view(n, G, dv)
-    q = unit_rms(rotate(q, positions, c.get("rot")), eps)
-    k = unit_rms(rotate(k, positions, c.get("rot")), eps)
-    o = talking_sink_attention(q, k, v, w[p + "talk"], c["scale"])
+    q = _r(h @ w[p + "q"].T).view(n, H, d)
+    k = _r(h @ w[p + "k"].T).view(n, G, d)
+    v = _r(h @ w[p + "v"].T).view(n, G, dv)
+    q = _r(unit_rms(rotate(q, positions, c.get("rot")), eps))
+    k = _r(unit_rms(rotate(k, positions, c.get("rot")), eps))
+    o = _r(talking_sink_attention(q, k, v, w[p + "talk"], c["scale"]))
     return o.reshape(n, H * dv) @ w[p + "o"].T
 
 
@@ -102,7 +112,7 @@ def mingru_branch(h, w: Dict[str, torch.Tensor], p: str, state: Optional[torch.T
         states.append(s)
     S = torch.stack(states)
     g = h @ w[p + "g"].T
-    return (S * (g * torch.sigmoid(g))) @ w[p + "o"].T, S
+    return _r(S * (g * torch.sigmoid(g))) @ w[p + "o"].T, S
 
 
 def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float) -> torch.Tensor:
@@ -111,7 +121,7 @@ def polynorm(z: torch.Tensor, coef: torch.Tensor, eps: float) -> torch.Tensor:
 
 
 def dense_ff(h, w, p: str, eps: float) -> torch.Tensor:
-    return polynorm(h @ w[p + "up"].T, w[p + "act"], eps) @ w[p + "down"].T
+    return _r(polynorm(h @ w[p + "up"].T, w[p + "act"], eps)) @ w[p + "down"].T
 
 
 def table_moe(h, tokens, w, p: str) -> torch.Tensor:
@@ -122,12 +132,22 @@ def table_moe(h, tokens, w, p: str) -> torch.Tensor:
         for e in table[int(tokens[t])].tolist():
             q = f"{p}e{int(e)}."
             g = h[t] @ w[q + "gate"].T
-            out[t] += ((g * torch.sigmoid(g)) * (h[t] @ w[q + "up"].T)) @ w[q + "down"].T / top
+            out[t] += _r((g * torch.sigmoid(g)) * (h[t] @ w[q + "up"].T)) @ w[q + "down"].T / top
     return out
 
 
-def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, dtype=torch.float64, layers_out: Optional[list] = None):
+def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, dtype=torch.float64, layers_out: Optional[list] = None,
+            round_to=None):
     """Logits [n, vocab] of one whole sequence; ``layers_out`` receives the stream after every layer."""
+    global _ROUND
+    _ROUND = round_to
+    try:
+        return _forward(cfg, w, tokens, dtype, layers_out)
+    finally:
+        _ROUND = None
+
+
+def _forward(cfg, w, tokens, dtype, layers_out):
     w = {k: (v.to(dtype) if v.is_floating_point() else v) for k, v in w.items()}
     eps = cfg["norm"]["eps"]
     tokens = torch.as_tensor(tokens, dtype=torch.long)
@@ -138,16 +158,53 @@ def forward(cfg: dict, w: Dict[str, torch.Tensor], tokens, dtype=torch.float64, 
         if layer["type"] != "parallel":
             raise ValueError(layer["type"])
         m = layer["mixer"]
-        h = norm_around_zero(x, w[p + "norm1"], eps)
+        h = _r(norm_around_zero(x, w[p + "norm1"], eps))
         left = attention_branch(h, pos, w, p + "mix.left.", m["left"], eps)
         right, _ = mingru_branch(h, w, p + "mix.right.")
         x = x + m["left_scale"] * left + m["right_scale"] * right
         if layer.get("mlp"):
-            h = norm_around_zero(x, w[p + "norm2"], eps)
+            h = _r(norm_around_zero(x, w[p + "norm2"], eps))
             if layer["mlp"]["kind"] == "dense":
                 x = x + dense_ff(h, w, p + "mlp.", eps)
             else:
                 x = x + table_moe(h, tokens, w, p + "mlp.")
         if layers_out is not None:
             layers_out.append(x.clone())
-    return norm_around_zero(x, w["final.norm"], eps) @ w["head"].T
+    return _r(norm_around_zero(x, w["final.norm"], eps)) @ w["head"].T
+
+
+def load_folder(folder: str):
+    """(config dict, weights dict) of a model folder, read with the standard library and numpy only."""
+    import json
+    import os
+    import struct
+    import numpy as np
+    with open(os.path.join(folder, "config.json")) as f:
+        cfg = json.load(f)
+    w = {}
+    with open(os.path.join(folder, "model.safetensors"), "rb") as f:
+        (n,) = struct.unpack("<Q", f.read(8))
+        header = json.loads(f.read(n))
+        data = f.read()
+    kinds = {"F32": (np.float32, torch.float32), "I32": (np.int32, torch.int32), "BF16": (np.uint16, torch.bfloat16)}
+    for name, info in header.items():
+        if name == "__metadata__":
+            continue
+        a, b = info["data_offsets"]
+        npdt, tdt = kinds[info["dtype"]]
+        arr = np.frombuffer(data[a:b], dtype=npdt).copy()
+        t = torch.from_numpy(arr)
+        if tdt == torch.bfloat16:
+            t = t.view(torch.bfloat16)
+        w[name] = t.reshape(info["shape"])
+    return cfg, w
+
+
+def generate(cfg: dict, w: Dict[str, torch.Tensor], prompt, steps: int) -> List[int]:
+    """Greedy continuation, the whole sequence recomputed for every token."""
+    seq, out = list(prompt), []
+    for _ in range(steps):
+        tok = int(forward(cfg, w, seq)[-1].argmax())
+        out.append(tok)
+        seq.append(tok)
+    return out
