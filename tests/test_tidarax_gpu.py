@@ -178,7 +178,7 @@ def _plain_attention(q, k, v, talk, scale, sink, window):
     return torch.einsum("hij,jhd->ihd", p, vv)
 
 
-def _attend(seqs, starts, talk, scale, sink, window, ps, dtype, bq=None, parts=1, out_scale=1.0, seed=0):
+def _attend(seqs, starts, talk, scale, sink, window, ps, dtype, bq=None, parts=1, out_scale=1.0, seed=0, mma=False):
     """seqs: (q, k, v) whole sequences; entry b brings the tokens from starts[b] on.  Returns per-entry outputs."""
     k_ = _k()
     H, d = seqs[0][0].shape[1:]
@@ -188,17 +188,18 @@ def _attend(seqs, starts, talk, scale, sink, window, ps, dtype, bq=None, parts=1
     T = sum(counts)
     qs = torch.cat([q[s:] for (q, _, _), s in zip(seqs, starts)]).to(dtype).to(DEV).contiguous()
     q_start = _i32(np.concatenate([[0], np.cumsum(counts)]).tolist())
-    pad = 5                                                       # the output sits inside a wider buffer
+    pad = 6 if mma else 5                                         # the output sits inside a wider buffer
     buf = torch.zeros(T, H * dv + pad, dtype=dtype, device=DEV)
     out = buf[:, 2:2 + H * dv]
     if bq is None:
-        bq = k_.attn_talking_tile(H, d, dv, max(counts))
+        bq = k_.attn_talking_mma_tile(H, G, d, dv, max(counts)) if mma else k_.attn_talking_tile(H, d, dv, max(counts))
+        assert bq > 0
     po = pml = None
     if parts > 1:
         po = torch.zeros(T * parts * H * dv, dtype=torch.float32, device=DEV)
         pml = torch.zeros(T * parts * H * 2, dtype=torch.float32, device=DEV)
     err = _err()
-    k_.attn_talking(out, qs, kc, vc, talk.float().to(DEV) if talk is not None else None, q_start, _i32(starts), len(seqs),
+    (k_.attn_talking_mma if mma else k_.attn_talking)(out, qs, kc, vc, talk.float().to(DEV) if talk is not None else None, q_start, _i32(starts), len(seqs),
                     table, stride, window, scale, sink, out_scale, bq, err, parts, po, pml)
     assert int(err.item()) == 0
     assert not buf[:, :2].any() and not buf[:, 2 + H * dv:].any()
@@ -232,6 +233,46 @@ def test_attention_equals_plain_for_unequal_entries(dtype, H, G, d, dv, sink, ta
     for (q, k, v), s, o in zip(seqs, starts, got):
         ref = _plain_attention(q, k, v, talk, scale, sink, window)[s:]
         assert (o - ref).abs().max() <= tol, (q.shape[0], s, float((o - ref).abs().max()))
+
+
+@pytest.mark.parametrize("H,G,d,dv", [(2, 1, 32, 16), (16, 4, 64, 64), (6, 2, 96, 64), (32, 8, 128, 128), (8, 8, 16, 16),
+                                      (12, 4, 48, 80), (3, 1, 32, 128), (64, 8, 64, 32), (10, 5, 16, 48)])
+@pytest.mark.parametrize("sink,talks,window", [(True, True, None), (False, True, 40), (True, False, None)])
+def test_tensor_core_attention_equals_plain(H, G, d, dv, sink, talks, window):
+    """The bfloat16 form whose two products run on tensor cores: whole prompts, continuations, a portion of two
+    tokens, single tokens (also cut into key ranges), against the plain implementation on the rounded operands."""
+    ps, scale = 16, 1.7 / math.sqrt(d)
+    g = torch.Generator().manual_seed(H * 7 + d)
+    talk = (torch.randn(H, H, generator=g, dtype=torch.float64) * (0.8 / math.sqrt(H)) + torch.eye(H)) if talks else None
+    plan = [(70, 0), (131, 90), (45, 43), (33, 32), (64, 63), (17, 16), (1, 0), (300, 281)]
+    seqs = [tuple(t.to(torch.bfloat16).double() for t in _random_qkv(n, H, G, d, dv, 10 * i + H)) for i, (n, _) in enumerate(plan)]
+    starts = [s for _, s in plan]
+    got = _attend(seqs, starts, talk, scale, sink, window, ps, torch.bfloat16, mma=True)
+    for (q, k, v), s, o in zip(seqs, starts, got):
+        ref = _plain_attention(q, k, v, talk, scale, sink, window)[s:]
+        assert (o - ref).abs().max() <= 2e-2, (q.shape[0], s, float((o - ref).abs().max()))
+    # single tokens, keys in ranges
+    singles = [(q, k, v) for (q, k, v) in seqs]
+    for parts in (1, 3):
+        got = _attend(singles, [q.shape[0] - 1 for q, _, _ in singles], talk, scale, sink, window, ps, torch.bfloat16, bq=1,
+                      parts=parts, out_scale=0.75, mma=True)
+        for (q, k, v), o in zip(singles, got):
+            ref = 0.75 * _plain_attention(q, k, v, talk, scale, sink, window)[-1:]
+            assert (o - ref).abs().max() <= 2e-2
+
+
+@pytest.mark.parametrize("where", ["first", "page_end", "page_start", "far", "self"])
+def test_tensor_core_attention_finds_a_planted_key(where):
+    H, G, d, dv, ps, n = 4, 2, 16, 16, 16, 600
+    j = {"first": 0, "page_end": 31, "page_start": 32, "far": n - 517, "self": n - 1}[where]
+    q, k, v = (t.to(torch.bfloat16).double() for t in _random_qkv(n, H, G, d, dv, 99))
+    for h in range(H):
+        q[-1, h] = k[j, h // (H // G)] * 3.0
+    for start, parts in ((n - 37, 1), (n - 1, 1), (n - 1, 4)):
+        got = _attend([(q, k, v)], [start], None, 1.0, True, None, ps, torch.bfloat16, parts=parts,
+                      bq=1 if start == n - 1 else None, mma=True)[0]
+        want = v[j].repeat_interleave(H // G, dim=0)
+        assert (got[-1] - want).abs().max() < 2e-2 * (1 + want.abs().max()), "the planted key must carry the output"
 
 
 @pytest.mark.parametrize("parts", [1, 2, 5, 16])

@@ -364,6 +364,14 @@ __global__ void attn_talking_merge_kernel(T* __restrict__ out, const float* __re
     }
 }
 
+// the merge alone, for the tensor-core form of the kernel (talking_attention_mma.cu)
+extern "C" int xb_attn_talking_merge_bf16(void* out, const float* part_o, const float* part_ml, int tokens, int H, int dv,
+                                          int parts, int ldo, float out_scale, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    attn_talking_merge_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>((__nv_bfloat16*)out, part_o, part_ml, H, dv, parts, ldo, out_scale);
+    return xb_launch_status();
+}
+
 static size_t talking_smem(int H, int d, int dv, int bq) {
     const int ldk = (d > dv ? d : dv) + 1;
     return ((size_t)bq * H * d + (size_t)TA_BK * ldk + 2 * (size_t)H * bq * TA_BK + (size_t)H * H + 3 * (size_t)H * bq) * sizeof(float);

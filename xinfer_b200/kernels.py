@@ -669,6 +669,39 @@ def attn_talking(out, q, k_cache, v_cache, talk, q_start, start_pos, num_entries
         int(parts), _ptr(part_o), _ptr(part_ml), err.data_ptr(), _stream()), "attn_talking", 2 if parts > 1 else 1)
 
 
+def attn_talking_mma_tile(nh: int, nkv: int, d: int, dv: int, want: int) -> int:
+    """The query tile the tensor-core form takes for these sizes (at most ``want``); 0: not its sizes."""
+    return int(kernels_lib().xb_attn_talking_mma_tile(int(nh), int(nkv), int(d), int(dv), int(max(want, 1))))
+
+
+def attn_talking_mma(out, q, k_cache, v_cache, talk, q_start, start_pos, num_entries, block_table, table_stride, window, scale,
+                     sink, out_scale, bq, err, parts: int = 1, part_o=None, part_ml=None):
+    """``attn_talking`` for bfloat16 with both products on tensor cores (mma.sync); the mix across heads, the
+    mask and the softmax stay float32 on the FMA units.  ``bq`` from ``attn_talking_mma_tile``; rows of ``out``
+    must start on 4-byte boundaries."""
+    T, nh, d = q.shape
+    _need(q, "q", torch.bfloat16, (T, nh, d))
+    _need(k_cache, "k_cache", torch.bfloat16, (None, None, None, d))
+    num_pages, nkv, ps, _ = k_cache.shape
+    dv = v_cache.shape[-1]
+    _need(v_cache, "v_cache", torch.bfloat16, (num_pages, nkv, ps, dv))
+    if (out.dtype != torch.bfloat16 or out.shape != (T, nh * dv) or out.stride(1) != 1 or not out.is_cuda
+            or out.stride(0) % 2 or out.data_ptr() % 4):
+        raise KernelError("out must be a bfloat16 view [T, heads * dv] with unit column stride and rows on 4-byte boundaries")
+    if talk is not None:
+        _need(talk, "talk", torch.float32, (nh, nh))
+    if parts > 1:
+        _need(part_o, "part_o", torch.float32)
+        _need(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < T * parts * nh * dv or part_ml.numel() < T * parts * nh * 2:
+            raise KernelError("attention scratch buffers are too small for the number of key ranges")
+    _ok(kernels_lib().xb_attn_talking_mma(
+        out.data_ptr(), int(out.stride(0)), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), _ptr(talk),
+        q_start.data_ptr(), start_pos.data_ptr(), int(num_entries), block_table.data_ptr(), int(table_stride), T, nh, nkv, d,
+        dv, ps, num_pages, int(window or 0), float(scale), int(bool(sink)), float(out_scale), int(bq), int(parts),
+        _ptr(part_o), _ptr(part_ml), err.data_ptr(), _stream()), "attn_talking_mma", 2 if parts > 1 else 1)
+
+
 def gated_scan(y, zxg, bz, bx, state, q_start, slots, req_of_token, num_entries, out_scale, scratch=None):
     """The minGRU recurrence over a step's tokens: ``zxg`` float32 ``[T, 3 * width]`` (the z, x and g
     projections without biases), ``state`` float32 ``[slots, width]`` carried per request, ``y`` a view

@@ -120,6 +120,8 @@ def _declare_kernels(lib):
     _sig(lib, "xb_qkv_prepare", I, [I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P])
     _sig(lib, "xb_attn_talking_tile", I, [I, I, I, I])
     _sig(lib, "xb_attn_talking", I, [I, P, I, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, I, F, I, I, P, P, P, P])
+    _sig(lib, "xb_attn_talking_mma_tile", I, [I, I, I, I, I])
+    _sig(lib, "xb_attn_talking_mma", I, [P, I, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, I, F, I, I, P, P, P, P])
     _sig(lib, "xb_gated_scan", I, [I, P, I, P, P, P, P, P, P, P, I, I, I, F, I, P, P])
     _sig(lib, "xb_polynorm", I, [I, P, P, P, I, I, F, P])
     _sig(lib, "xb_expert_route", I, [P, P, P, P, P, P, I, P, I, I, I, I, P, P])

@@ -27,6 +27,8 @@ _DEFAULT_NAMES = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.wei
 # a single-token step cuts every token's keys into ranges so that about this many blocks run
 _DECODE_BLOCKS = 296
 _DECODE_MIN_KEYS = 128
+# bfloat16: both products on tensor cores where the sizes allow; tests switch it off to compare the two forms
+USE_TENSOR_CORES = True
 
 
 class TalkingAttention(Mixer):
@@ -103,11 +105,13 @@ class TalkingAttention(Mixer):
         # and cuts the keys instead); a replayed step must not look at its actual lengths
         single = ctx.all_single or ctx.fixed_shapes
         longest = 1 if single else int((ctx.h_q_start[1:] - ctx.h_q_start[:-1]).max())
-        bq = kernels.attn_talking_tile(nh, d, dv, longest)
+        mma = (USE_TENSOR_CORES and self.dtype == torch.bfloat16 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0
+               and kernels.attn_talking_mma_tile(nh, nkv, d, dv, longest) > 0)
+        bq = kernels.attn_talking_mma_tile(nh, nkv, d, dv, longest) if mma else kernels.attn_talking_tile(nh, d, dv, longest)
         if bq <= 0:
             raise kernels.KernelError(f"attention with {nh} heads of {d}/{dv} channels does not fit the kernel's tile")
         parts, part_o, part_ml = 1, None, None
-        if single and bq == 1:
+        if single and bq == 1:      # (a single-token step always gets a tile of one query)
             bound = stride * cache.page_size if ctx.fixed_shapes else ctx.max_context
             if s.window:
                 bound = min(bound, s.window + 32)
@@ -115,7 +119,7 @@ class TalkingAttention(Mixer):
             if parts > 1:
                 part_o = ws.get("tattn.part_o", (T * parts * nh * dv,), torch.float32)
                 part_ml = ws.get("tattn.part_ml", (T * parts * nh * 2,), torch.float32)
-        kernels.attn_talking(out, q, cache["k"], cache["v"], self.talk, ctx.q_start, ctx.start_pos, ctx.num_entries, table,
+        (kernels.attn_talking_mma if mma else kernels.attn_talking)(out, q, cache["k"], cache["v"], self.talk, ctx.q_start, ctx.start_pos, ctx.num_entries, table,
                              stride, s.window, s.scale, s.sink, out_scale, bq, ctx.err, parts, part_o, part_ml)
 
     def forward(self, x, ctx: StepContext, cache: LayerCache, state=None, writes_cache: bool = True):
