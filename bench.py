@@ -6,6 +6,7 @@
     python bench.py --kernels                               # single kernels at serving sizes
     python bench.py --kernels --attn 16,8,64                # the attention kernels at another head layout
     python bench.py --ablate                                # a decode step with one kind of kernel left out at a time
+    python bench.py --compare tidarax [--size 1k|4k]        # the Tidarax design beside Qwen3 at equal layer sizes
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and the context length
 of the configuration (a "step" is one decode step of the whole batch), timed on the device with
@@ -205,6 +206,92 @@ def mixed_workload(args, cfg, full, pk) -> int:
     return 0
 
 
+# Layer sizes for --compare: a Tidarax model and a Qwen3 model of the same width, heads, head size and
+# feed-forward size (the recurrence as wide as the model, experts a quarter of the dense feed-forward each).
+COMPARE_SIZES = {
+    "1k": dict(hidden=1024, heads=16, kv_heads=8, head_dim=128, intermediate=3072, experts=8, expert_ff=768, top=2),
+    "4k": dict(hidden=4096, heads=32, kv_heads=8, head_dim=128, intermediate=12288, experts=8, expert_ff=3072, top=2),
+}
+
+
+def tidarax_config(z: dict, layers: int, vocab: int) -> dict:
+    left = dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=z["head_dim"], vdim=z["head_dim"], scale=z["head_dim"] ** -0.5,
+                rot=dict(dims=z["head_dim"], base=500000.0, scaling=dict(factor=8.0, low=1.0, high=4.0, original=8192)))
+    mixer = dict(left=left, left_scale=1.0, right=dict(width=z["hidden"]), right_scale=1.0)
+    dense = dict(kind="dense", ff=z["intermediate"])
+    moe = dict(kind="moe", expert=dict(ff=z["expert_ff"]), router=dict(experts=z["experts"], top=z["top"]))
+    return dict(architecture="Tidarax", vocab=vocab, width=z["hidden"], norm=dict(eps=1e-6),
+                layers=[dict(type="parallel", mixer=mixer, mlp=dense if i % 2 == 0 else moe) for i in range(layers)])
+
+
+def compare(args) -> int:
+    """Prefill and decode throughput of a Tidarax model and of a Qwen3 model of the same layer sizes (random
+    weights, `--layers` layers each, default 4), then the Tidarax kernels one by one beside their like kernels.
+    One JSON line per model and per kernel."""
+    import numpy as np
+    import torch
+    from xinfer_b200 import measure
+    from xinfer_b200.engine.runner import ModelRunner, StepInput
+    pk = peaks()
+    z = COMPARE_SIZES[args.size]
+    L, V, B, ctx_len = args.layers or 4, 32000, args.batch, 2048
+    models = {
+        "Tidarax": tidarax_config(z, L, V),
+        "Qwen3": dict(CONFIG, vocab_size=V, hidden_size=z["hidden"], intermediate_size=z["intermediate"], num_hidden_layers=L,
+                      num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["head_dim"]),
+    }
+    rng = np.random.default_rng(0)
+    for name, cfg in models.items():
+        pages = (ctx_len + 64 + PAGE - 1) // PAGE + 1
+        runner = ModelRunner.random(cfg, seed=0, dtype="bfloat16", block_size=PAGE, num_blocks=(B + 1) * pages, max_num_seqs=B + 1,
+                                    max_model_len=ctx_len + 128)
+        pre = []
+        for i in range(5):
+            s = runner.open_request()
+            ids = rng.integers(0, V, size=PREFILL_TOKENS)
+            torch.cuda.synchronize()
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            e0.record()
+            logits = runner.step([StepInput(s, ids, [PREFILL_TOKENS - 1])])
+            e1.record()
+            torch.cuda.synchronize()
+            if i == 0:
+                check_finite(logits, f"the first prefill of {name}")
+            if i >= 2:
+                pre.append(e0.elapsed_time(e1))
+            runner.close_request(s)
+        slots = [runner.open_request() for _ in range(B)]
+        for s in slots:
+            runner.step([StepInput(s, rng.integers(0, V, size=ctx_len - 64), [])])
+        steps, warm = 32, 8 + SETTLE
+        toks = rng.integers(0, V, size=(steps + warm, B))
+        for i in range(warm):
+            runner.step([StepInput(s, toks[i, j:j + 1], [0]) for j, s in enumerate(slots)], allow_graph=not args.no_graph)
+        torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(warm, warm + steps):
+            logits = runner.step([StepInput(s, toks[i, j:j + 1], [0]) for j, s in enumerate(slots)], allow_graph=not args.no_graph)
+        e1.record()
+        torch.cuda.synchronize()
+        runner.check_errors()
+        check_finite(logits, f"the last decode step of {name}")
+        ms = e0.elapsed_time(e1) / steps
+        print(json.dumps({"model": name, "size": args.size, "layers": L, "weight_gb": round(runner.model.weight_bytes() / 1e9, 3),
+                          "prefill_tokens": PREFILL_TOKENS, "prefill_ms": round(min(pre), 3),
+                          "prefill_tok_s": round(PREFILL_TOKENS / (min(pre) / 1e3), 1), "decode_batch": B,
+                          "decode_context": ctx_len, "decode_ms_per_step": round(ms, 4), "decode_tok_s": round(B / (ms / 1e3), 1),
+                          "launches_per_decode_step": runner.last_launches, "cuda_graph": runner.last_used_graph,
+                          "dtype": "bf16", "data": "synthetic (random weights, seeded uniform token ids)"}), flush=True)
+        del runner
+        torch.cuda.empty_cache()
+    for rec in measure.tidarax_kernels(hidden=z["hidden"], heads=z["heads"], kv_heads=z["kv_heads"], head_dim=z["head_dim"],
+                                       intermediate=z["intermediate"], rec_width=z["hidden"], experts=z["experts"],
+                                       expert_ff=z["expert_ff"], top=z["top"], hbm_gbs=pk["hbm_gbs"], peak_tflops=pk["bf16_tflops"]):
+        print(json.dumps(dict(rec, size=args.size)), flush=True)
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -228,6 +315,10 @@ def main() -> int:
                     help="with --kernels: the attention kernels alone at this head layout, over short and long contexts")
     ap.add_argument("--case", default="", metavar="decode:BATCHxCONTEXT | prefill:CACHED+NEW",
                     help="with --kernels --attn: this one case instead of the standard ones")
+    ap.add_argument("--compare", default="", choices=["", "tidarax"],
+                    help="instead of the step benchmark: prefill and decode throughput of this design beside Qwen3 at equal "
+                         "layer sizes, and its kernels beside their like kernels; one JSON line each")
+    ap.add_argument("--size", default="4k", choices=sorted(COMPARE_SIZES), help="layer sizes of --compare")
     ap.add_argument("--kernels", action="store_true",
                     help="instead of the step benchmark, time single kernels at serving sizes: one JSON line each")
     args = ap.parse_args()
@@ -237,6 +328,8 @@ def main() -> int:
         print("bench.py: this engine runs on one GPU; --gpus must be 1")
         return 2
     steps, warmup = max(args.steps, 1), max(args.warmup, 3)
+    if args.compare:
+        return compare(args)
     if args.ablate:
         from xinfer_b200 import measure
         for rec in measure.decode_ablation(dict(CONFIG, **SHAPES[args.shape]), layers=args.layers or 12):

@@ -405,10 +405,12 @@ def test_polynorm_equals_plain(out_dtype):
 # ---------------------------------------------------------------------------------------------
 # experts by table
 # ---------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("E,top,ff,hid,T", [(5, 2, 24, 48, 77), (8, 1, 40, 64, 3), (3, 3, 16, 32, 130), (16, 4, 72, 96, 1)])
-def test_table_experts_equal_plain(dtype, E, top, ff, hid, T):
+@pytest.mark.parametrize("dtype,tensor_cores", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
+@pytest.mark.parametrize("E,top,ff,hid,T", [(5, 2, 24, 48, 77), (8, 1, 40, 64, 3), (3, 3, 16, 32, 130), (16, 4, 72, 96, 1),
+                                            (4, 2, 200, 136, 300), (2, 1, 60, 44, 9)])
+def test_table_experts_equal_plain(dtype, tensor_cores, E, top, ff, hid, T, monkeypatch):
     from xinfer_b200.config.plan import ExpertTableSpec
+    monkeypatch.setattr(_k(), "expert_tensor_cores", tensor_cores)
     from xinfer_b200.parts import StepContext, Workspace, build_part
     vocab = 41
     g = torch.Generator().manual_seed(E * 10 + top)

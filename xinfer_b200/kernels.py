@@ -748,6 +748,10 @@ def expert_route(offsets, perm, inv, table, ids, sampled, req_of_token, tokens, 
         "expert_route")
 
 
+# bfloat16 grouped products on tensor cores where the sizes allow; tests switch it off to compare the two forms
+expert_tensor_cores = True
+
+
 def expert_gemm(y, a, w, offsets, perm, gather: bool, top: int, gated: bool):
     """y[r] = a[src(r)] . w[e(r)]^T over rows grouped by expert (``expert_route``); ``w`` is
     ``[experts, N, K]`` (``[experts, 2 N, K]`` when ``gated``: y = silu(gate) * up)."""
@@ -758,6 +762,13 @@ def expert_gemm(y, a, w, offsets, perm, gather: bool, top: int, gated: bool):
     _need(w, "w", a.dtype, (E, None, K))
     _need(a, "a", None, (None, K))
     _need(y, "y", None, (rows, N))
+    if expert_tensor_cores and a.dtype == torch.bfloat16 and K % 8 == 0:
+        rc = kernels_lib().xb_expert_gemm_mma(dtype_code(y.dtype), y.data_ptr(), a.data_ptr(), w.data_ptr(), offsets.data_ptr(),
+                                              perm.data_ptr(), int(bool(gather)), int(top), E, rows, N, K, int(bool(gated)),
+                                              _stream())
+        if rc != ERR_NOT_SUPPORTED:
+            _ok(rc, "expert_gemm_mma")
+            return
     _ok(kernels_lib().xb_expert_gemm(dtype_code(a.dtype), dtype_code(y.dtype), y.data_ptr(), a.data_ptr(), w.data_ptr(),
                                      offsets.data_ptr(), perm.data_ptr(), int(bool(gather)), int(top), E, rows, N, K,
                                      int(bool(gated)), _stream()), "expert_gemm")

@@ -315,3 +315,147 @@ def decode_ablation(config: Dict, *, layers: int = 12, batches: Sequence[int] = 
         (kernels.swiglu, kernels.qk_norm_rope_write, backend.attend, attention_part.linear, swiglu_part.linear) = keep[:5]
         norm_part.RMSNorm.forward = keep[5]
     return out
+
+
+# ---- the Tidarax kernels at a real model's layer sizes, each beside the like kernel of the Qwen3 path ----------
+FP32_FMA_TFLOPS_NOMINAL = 148 * 128 * 2 * 1.965e9 / 1e12      # 148 SMs x 128 lanes x 2 operations at 1965 MHz
+
+
+def tidarax_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, head_dim: int = 128, intermediate: int = 12288,
+                    rec_width: int = 4096, experts: int = 8, expert_ff: int = 3072, top: int = 2, tokens: int = 2048,
+                    decode: Sequence[int] = (8, 4096), page_size: int = 16, hbm_gbs: float = 0.0, peak_tflops: float = 0.0,
+                    device="cuda:0") -> List[Dict]:
+    """One record per kernel of the Tidarax path: time, what it achieves and the share of its floor.  The
+    floor of the attention is the slower of its tensor-core products at the measured matrix-product peak
+    and its mix across heads (2 heads^2 float32 operations per query-key pair) at the nominal FMA rate."""
+    out: List[Dict] = []
+    err = torch.zeros(1, dtype=torch.int32, device=device)
+    bf = lambda *shape: torch.randn(*shape, device=device).bfloat16()
+    H, G, d = heads, kv_heads, head_dim
+    talk = (torch.randn(H, H, device=device) / H ** 0.5).float().contiguous()
+
+    # attention over a whole prompt
+    ctx, table, stride, num_pages = _attention_context([(0, tokens)], page_size, device)
+    kc, vc = bf(num_pages, G, page_size, d), bf(num_pages, G, page_size, d)
+    q, o = bf(tokens, H, d), torch.empty(tokens, H * d, dtype=torch.bfloat16, device=device)
+    pairs = tokens * (tokens + 1) / 2
+    for name, fn, tile in (("tensor cores", kernels.attn_talking_mma, kernels.attn_talking_mma_tile(H, G, d, d, tokens)),
+                           ("FMA units", kernels.attn_talking, kernels.attn_talking_tile(H, d, d, tokens))):
+        if tile <= 0 or (name == "FMA units" and tokens * H * d > 2048 * 16 * 128):
+            continue      # the FMA form at these sizes takes seconds: it is the float32 path's kernel
+        us = _graph_time_us(lambda: fn(o, q, kc, vc, talk, ctx.q_start, ctx.start_pos, 1, table, stride, None, d ** -0.5,
+                                       True, 1.0, tile, err), 1, repeats=5)
+        tc, mix = 4.0 * H * d * pairs, 2.0 * H * H * pairs
+        floor_us = max(tc / (peak_tflops or 1590.0) / 1e6, mix / FP32_FMA_TFLOPS_NOMINAL / 1e6)
+        out.append({"kernel": f"talking attention, prompt ({name})", "tokens": tokens, "us": round(us, 1),
+                    "tensor_tflops": round(tc / us / 1e6, 1), "mix_fp32_tflops": round(mix / us / 1e6, 2),
+                    "floor_us": round(floor_us, 1), "frac_of_floor": round(floor_us / us, 3), "query_tile": tile})
+    like = prefill_attention(((0, tokens),), heads=H, kv_heads=G, head_dim=d, page_size=page_size, peak_tflops=peak_tflops)[0]
+    out.append({"kernel": "like: Qwen3 prompt attention (tcgen05)", "tokens": tokens, "us": like["tcgen05_us"],
+                "tensor_tflops": like["tflops"], "frac_of_floor": like.get("frac_of_peak")})
+
+    # attention of single tokens
+    batch, context = decode
+    ctx, table, stride, num_pages = _attention_context([(context - 1, 1)] * batch, page_size, device)
+    layers = 4
+    caches = [(bf(num_pages, G, page_size, d), bf(num_pages, G, page_size, d)) for _ in range(layers)]
+    q, o = bf(batch, H, d), torch.empty(batch, H * d, dtype=torch.bfloat16, device=device)
+    parts = max(1, min(296 // batch, context // 128, 64))
+    po = torch.zeros(batch * parts * H * d, dtype=torch.float32, device=device)
+    pml = torch.zeros(batch * parts * H * 2, dtype=torch.float32, device=device)
+    nbytes = batch * context * G * d * 2 * 2
+    us = _graph_time_us(lambda: [kernels.attn_talking_mma(o, q, k_, v_, talk, ctx.q_start, ctx.start_pos, batch, table, stride,
+                                                          None, d ** -0.5, True, 1.0, 1, err, parts, po, pml)
+                                 for k_, v_ in caches], layers)
+    floor_us = nbytes / (hbm_gbs or 6650.0) / 1e3
+    out.append({"kernel": "talking attention, single tokens (tensor cores)", "batch": batch, "context": context,
+                "us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1), "floor_us": round(floor_us, 1),
+                "frac_of_floor": round(floor_us / us, 3), "key_ranges": parts})
+    like = decode_attention(((batch, context),), heads=H, kv_heads=G, head_dim=d, page_size=page_size, hbm_gbs=hbm_gbs)[0]
+    out.append({"kernel": "like: Qwen3 single-token attention (tcgen05)", "batch": batch, "context": context,
+                "us": like["tcgen05_us"], "gbs": like["gbs"], "frac_of_floor": like.get("frac_of_hbm")})
+    del caches, po, pml
+
+    # the memory-bound kernels at a prompt portion's size; several sets of buffers, together larger than the L2
+    sets = 4
+
+    def record(name, nbytes, run, like=None):
+        us = _loop_time_us(lambda: [run(i) for i in range(sets)]) / sets
+        rec = {"kernel": name, "tokens": tokens, "bytes": nbytes, "us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1)}
+        if hbm_gbs:
+            rec["frac_of_floor"] = round(rec["gbs"] / hbm_gbs, 3)
+        if like:
+            rec["like"] = like
+        out.append(rec)
+
+    xs = [torch.randn(tokens, hidden, device=device) for _ in range(sets)]
+    bs = [torch.randn(tokens, hidden, device=device) for _ in range(sets)]
+    os_ = [torch.empty(tokens, hidden, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    w = torch.randn(hidden, device=device)
+    record("float32 residual sum + norm", tokens * hidden * (4 + 4 + 4 + 2),
+           lambda i: kernels.rmsnorm(os_[i], xs[i], w, 1e-6, err, branch=bs[i], sum_out=xs[i], weight_offset=1.0),
+           "residual sum + RMSNorm")
+    del xs, bs, os_
+    width = (H + 2 * G) * d
+    qkvs = [bf(tokens, width) for _ in range(sets)]
+    qs = [torch.empty(tokens, H, d, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    pages = (tokens + page_size - 1) // page_size
+    kcs = [torch.zeros(pages, G, page_size, d, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    vcs = [torch.zeros_like(k) for k in kcs]
+    inv = torch.rand(d // 2, device=device)
+    pos = torch.arange(tokens, dtype=torch.int32, device=device)
+    req = torch.zeros(tokens, dtype=torch.int32, device=device)
+    tab = torch.randperm(pages, device=device).to(torch.int32)
+    record("rotation + unit norm + cache write", 2 * tokens * width * 2,
+           lambda i: kernels.qkv_prepare(qs[i], kcs[i], vcs[i], qkvs[i], None, None, inv, pos, req, tab, pages, H, G, d, d, d,
+                                         False, 2, 1e-6, True, err), "q/k norm + rotation + cache write")
+    del qkvs, qs, kcs, vcs
+    W = rec_width
+    zxgs = [torch.randn(tokens, 3 * W, device=device) for _ in range(sets)]
+    ys = [torch.empty(tokens, W, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    bz, bx = torch.randn(W, device=device), torch.randn(W, device=device)
+    state = torch.zeros(2, W, device=device)
+    q_start = torch.tensor([0, tokens], dtype=torch.int32, device=device)
+    slots = torch.tensor([0], dtype=torch.int32, device=device)
+    scratch = torch.empty(3 * tokens * W, device=device)
+    record("gated recurrence over a prompt (three passes)", tokens * W * (3 * 4 + 2),
+           lambda i: kernels.gated_scan(ys[i], zxgs[i], bz, bx, state, q_start, slots, req, 1, 1.0, scratch), "SiLU gate")
+    del zxgs, ys, scratch
+    zs = [torch.randn(tokens, intermediate, device=device) for _ in range(sets)]
+    acts = [torch.empty(tokens, intermediate, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    coef = torch.tensor([0.5, 0.3, 0.2, 0.1], device=device)
+    record("polynomial activation with normed powers", tokens * intermediate * (4 + 2),
+           lambda i: kernels.polynorm(acts[i], zs[i], coef, 1e-6), "SiLU gate")
+    del zs, acts
+    for rec in prefill_elementwise(tokens, hidden=hidden, heads=H, kv_heads=G, head_dim=d, intermediate=intermediate,
+                                   page_size=page_size, hbm_gbs=hbm_gbs):
+        out.append({"kernel": "like: Qwen3 " + rec["kernel"], "tokens": tokens, "us": rec["us"], "gbs": rec["gbs"],
+                    "frac_of_floor": rec.get("frac_of_hbm")})
+
+    # the experts' grouped products against the library's dense product of the same work
+    E, F = experts, expert_ff
+    rows = tokens * top
+    x = bf(tokens, hidden)
+    wgu, wd = bf(E, 2 * F, hidden) * 0.02, bf(E, hidden, F) * 0.02
+    table = torch.rand(1000, E, device=device).argsort(dim=1)[:, :top].to(torch.int32).contiguous()
+    ids = torch.randint(0, 1000, (tokens,), device=device, dtype=torch.int32)
+    offsets = torch.zeros(E + 1, dtype=torch.int32, device=device)
+    perm, inv_ = torch.zeros(rows, dtype=torch.int32, device=device), torch.zeros(rows, dtype=torch.int32, device=device)
+    kernels.expert_route(offsets, perm, inv_, table, ids, None, req, tokens, top, E, err)
+    act, y = torch.empty(rows, F, dtype=torch.bfloat16, device=device), torch.empty(rows, hidden, device=device)
+    us1 = _loop_time_us(lambda: kernels.expert_gemm(act, x, wgu, offsets, perm, True, top, True))
+    us2 = _loop_time_us(lambda: kernels.expert_gemm(y, act, wd, offsets, perm, False, top, False))
+    us0 = _loop_time_us(lambda: kernels.expert_route(offsets, perm, inv_, table, ids, None, req, tokens, top, E, err))
+    f1, f2 = 2.0 * rows * 2 * F * hidden, 2.0 * rows * hidden * F
+    for name, us, fl in (("experts: gate/up product with the gate (mma.sync)", us1, f1), ("experts: down product (mma.sync)", us2, f2)):
+        out.append({"kernel": name, "rows": rows, "us": round(us, 1), "tensor_tflops": round(fl / us / 1e6, 1),
+                    "frac_of_floor": round(fl / us / 1e6 / (peak_tflops or 1590.0), 3)})
+    out.append({"kernel": "experts: grouping by expert (one block)", "rows": rows, "us": round(us0, 1)})
+    xa, wa = bf(rows, hidden), bf(2 * F, hidden)
+    oa = torch.empty(rows, 2 * F, dtype=torch.bfloat16, device=device)
+    usl = _loop_time_us(lambda: torch.mm(xa, wa.t(), out=oa))
+    out.append({"kernel": "like: the library's dense product of the gate/up work", "rows": rows, "us": round(usl, 1),
+                "tensor_tflops": round(f1 / usl / 1e6, 1), "frac_of_floor": round(f1 / usl / 1e6 / (peak_tflops or 1590.0), 3)})
+    if int(err):
+        raise RuntimeError("a kernel reported an error: " + kernels.describe_error(int(err)))
+    return out
