@@ -1,7 +1,7 @@
 // The grouped product of the table-routed experts (see expert_table.cu) for bfloat16 on tensor cores:
 // y[r] = a[src(r)] . w[e(r)]^T over rows grouped by expert, mma.sync m16n8k16 tiles with float32 accumulators.
-// A block takes 64 rows of ONE expert and 128 rows of that expert's matrix (gated: 64 columns of gate and the
-// same 64 of up, finished as silu(gate) * up in the accumulators); K runs in panels of 32 through two
+// A block takes 128 rows of ONE expert and 128 rows of that expert's matrix (gated: 64 columns of gate and the
+// same 64 of up, finished as silu(gate) * up in the accumulators); K runs in panels of 32 through three
 // shared-memory stages filled by 16-byte asynchronous copies.  A row's sum runs over K in the same order
 // whatever shares its tile, so a token's result does not depend on its company.
 #include "common.cuh"
@@ -9,7 +9,10 @@
 
 using namespace xbmma;
 
-constexpr int EG_BM = 64, EG_BN = 128, EG_BK = 32, EG_LD = EG_BK + 8, EG_THREADS = 256;
+constexpr int EG_BM = 128, EG_BN = 128, EG_BK = 32, EG_LD = EG_BK + 8, EG_THREADS = 256, EG_STAGES = 3;
+constexpr size_t EG_SMEM = (size_t)EG_STAGES * (EG_BM + EG_BN) * EG_LD * sizeof(__nv_bfloat16);
+
+__device__ __forceinline__ void eg_wait_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
 
 template <typename TO, bool GATED>
 __global__ void __launch_bounds__(EG_THREADS) expert_gemm_mma_kernel(TO* __restrict__ y, const __nv_bfloat16* __restrict__ a,
@@ -17,8 +20,10 @@ __global__ void __launch_bounds__(EG_THREADS) expert_gemm_mma_kernel(TO* __restr
                                                                      const int* __restrict__ offsets,
                                                                      const int* __restrict__ perm, int gather, int top, int E,
                                                                      int N, int K) {
-    __shared__ __align__(16) __nv_bfloat16 As[2][EG_BM][EG_LD];
-    __shared__ __align__(16) __nv_bfloat16 Bs[2][EG_BN][EG_LD];
+    extern __shared__ __align__(16) unsigned char eg_smem[];
+    typedef __nv_bfloat16 (*Tile)[EG_BM][EG_LD];            // EG_BM == EG_BN
+    Tile As = reinterpret_cast<Tile>(eg_smem);
+    Tile Bs = reinterpret_cast<Tile>(eg_smem + (size_t)EG_STAGES * EG_BM * EG_LD * sizeof(__nv_bfloat16));
     __shared__ int s_e, s_row0, s_rows;
     __shared__ int src[EG_BM];
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
@@ -46,10 +51,10 @@ __global__ void __launch_bounds__(EG_THREADS) expert_gemm_mma_kernel(TO* __restr
     constexpr int COLS = GATED ? EG_BN / 2 : EG_BN;           // output columns of a block
     const int n0 = blockIdx.x * COLS;
     const __nv_bfloat16* we = w + (size_t)e * (GATED ? 2 : 1) * N * K;
-    const int wm = warp >> 2, wn = warp & 3;                  // 2 x 4 warps: 32 rows x 32 matrix rows each
+    const int wm = warp >> 1, wn = warp & 1;                  // 4 x 2 warps: 32 rows x 64 matrix rows each
 
     auto load = [&](int stage, int k0) {
-        // A: 64 rows x 4 pieces of 8; B: 128 rows x 4 pieces
+        // A: 128 rows x 4 pieces of 8; B: 128 rows x 4 pieces
         for (int idx = tid; idx < (EG_BM + EG_BN) * 4; idx += EG_THREADS) {
             const int r = idx >> 2, c = (idx & 3) * 8;
             const int gk = k0 + c;
@@ -68,20 +73,21 @@ __global__ void __launch_bounds__(EG_THREADS) expert_gemm_mma_kernel(TO* __restr
         cp_async_commit();
     };
 
-    float acc[2][4][4];
+    float acc[2][8][4];
 #pragma unroll
     for (int i = 0; i < 2; ++i)
 #pragma unroll
-        for (int j = 0; j < 4; ++j)
+        for (int j = 0; j < 8; ++j)
 #pragma unroll
             for (int c = 0; c < 4; ++c) acc[i][j][c] = 0.f;
     const int panels = (K + EG_BK - 1) / EG_BK;
     load(0, 0);
+    if (panels > 1) load(1, EG_BK); else cp_async_commit();
     for (int p = 0; p < panels; ++p) {
-        const int st = p & 1;
-        cp_async_wait_all();
-        __syncthreads();                                      // panel p has landed; everyone is done with panel p - 1
-        if (p + 1 < panels) load(st ^ 1, (p + 1) * EG_BK);
+        const int st = p % EG_STAGES;
+        eg_wait_but_one();                                    // panel p has landed (panel p + 1 may still be on its way)
+        __syncthreads();                                      // ... for everyone, and everyone is done with panel p - 1
+        if (p + 2 < panels) load((p + 2) % EG_STAGES, (p + 2) * EG_BK); else cp_async_commit();
 #pragma unroll
         for (int ks = 0; ks < EG_BK / 16; ++ks) {
             uint32_t af[2][4];
@@ -89,8 +95,9 @@ __global__ void __launch_bounds__(EG_THREADS) expert_gemm_mma_kernel(TO* __restr
             for (int i = 0; i < 2; ++i)
                 ldmatrix_x4(af[i], smem_addr(&As[st][wm * 32 + i * 16 + (lane & 15)][ks * 16 + (lane >> 4) * 8]));
 #pragma unroll
-            for (int jp = 0; jp < 2; ++jp) {                  // a pair of 8-row tiles of the matrix
-                const int base = GATED ? jp * 64 + wn * 16 : wn * 32 + jp * 16;
+            for (int jp = 0; jp < 4; ++jp) {                  // a pair of 8-row tiles of the matrix
+                // gated: pairs 0, 1 are gate columns wn * 32 .., pairs 2, 3 the same columns of up
+                const int base = GATED ? (jp >> 1) * 64 + wn * 32 + (jp & 1) * 16 : wn * 64 + jp * 16;
                 uint32_t bf[4];
                 ldmatrix_x4(bf, smem_addr(&Bs[st][base + (lane & 7) + ((lane >> 4) << 3)][ks * 16 + ((lane >> 3) & 1) * 8]));
 #pragma unroll
@@ -110,21 +117,21 @@ __global__ void __launch_bounds__(EG_THREADS) expert_gemm_mma_kernel(TO* __restr
             TO* yr = y + (size_t)(row0 + r) * N;
             if (GATED) {
 #pragma unroll
-                for (int j = 0; j < 2; ++j)
+                for (int j = 0; j < 4; ++j)
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
-                        const int col = n0 + wn * 16 + j * 8 + (lane & 3) * 2 + c;
+                        const int col = n0 + wn * 32 + j * 8 + (lane & 3) * 2 + c;
                         if (col < N) {
-                            const float g = acc[i][j][half * 2 + c], u = acc[i][2 + j][half * 2 + c];
+                            const float g = acc[i][j][half * 2 + c], u = acc[i][4 + j][half * 2 + c];
                             yr[col] = from_f32<TO>(g / (1.f + expf(-g)) * u);
                         }
                     }
             } else {
 #pragma unroll
-                for (int j = 0; j < 4; ++j)
+                for (int j = 0; j < 8; ++j)
 #pragma unroll
                     for (int c = 0; c < 2; ++c) {
-                        const int col = n0 + wn * 32 + j * 8 + (lane & 3) * 2 + c;
+                        const int col = n0 + wn * 64 + j * 8 + (lane & 3) * 2 + c;
                         if (col < N) yr[col] = from_f32<TO>(acc[i][j][half * 2 + c]);
                     }
             }
@@ -139,7 +146,12 @@ XB_EXPORT int xb_expert_gemm_mma(int out_dtype, void* y, const void* a, const vo
     typedef __nv_bfloat16 bf;
     const int cols = gated ? EG_BN / 2 : EG_BN;
     const dim3 grid((N + cols - 1) / cols, (rows_max + EG_BM - 1) / EG_BM + experts);
-#define XB_EG(TO, G) expert_gemm_mma_kernel<TO, G><<<grid, EG_THREADS, 0, stream>>>((TO*)y, (const bf*)a, (const bf*)w, offsets, perm, gather, top, experts, N, K)
+#define XB_EG(TO, G)                                                                                                          \
+    do {                                                                                                                      \
+        cudaFuncSetAttribute(expert_gemm_mma_kernel<TO, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)EG_SMEM);       \
+        expert_gemm_mma_kernel<TO, G><<<grid, EG_THREADS, EG_SMEM, stream>>>((TO*)y, (const bf*)a, (const bf*)w, offsets, perm, \
+                                                                            gather, top, experts, N, K);                      \
+    } while (0)
     if (out_dtype == XB_F32) {
         if (gated) XB_EG(float, true); else XB_EG(float, false);
     } else {

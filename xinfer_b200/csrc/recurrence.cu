@@ -53,7 +53,7 @@ __global__ void gated_scan_serial_kernel(T* __restrict__ y, int ldy, const float
 
 // chunked form.  Chunks are counted over the step's rows: chunk k covers rows [k*CH, (k+1)*CH); a chunk
 // that crosses an entry's border is handled per entry by restarting at the border (req_of_token tells).
-constexpr int GS_CH = 64;
+constexpr int GS_CH = 32;
 
 // pass 1: per (chunk, channel), for every entry piece inside the chunk: A = prod a, Bv = value from zero.
 // A chunk holds at most a few pieces; to keep it simple a piece is identified by its first row, and
@@ -95,13 +95,31 @@ __global__ void gated_scan_starts_kernel(float* __restrict__ start, const float*
     const int t0 = q_start[b], t1 = q_start[b + 1];
     if (t1 <= t0) return;
     float S = state[(size_t)slot * W + c];
+    // pieces: [t0, first chunk border), then whole chunks, then the rest; four pieces' pairs are loaded ahead
+    // of the recurrence, which only needs them one after the other
     int t = t0;
     while (t < t1) {
-        const int piece_end = min(t1, (t / GS_CH + 1) * GS_CH);     // rows [t, piece_end) are one piece
-        start[(size_t)t * W + c] = S;
-        const size_t last = (size_t)(piece_end - 1) * W + c;
-        S = fmaf(prodA[last], S, endB[last]);
-        t = piece_end;
+        int first[4], last[4];
+        float A[4], B[4];
+        int n = 0;
+        for (int tt = t; n < 4 && tt < t1; ++n) {
+            first[n] = tt;
+            tt = min(t1, (tt / GS_CH + 1) * GS_CH);
+            last[n] = tt - 1;
+        }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (k < n) {
+                A[k] = prodA[(size_t)last[k] * W + c];
+                B[k] = endB[(size_t)last[k] * W + c];
+            }
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+            if (k < n) {
+                start[(size_t)first[k] * W + c] = S;
+                S = fmaf(A[k], S, B[k]);
+            }
+        t = last[n - 1] + 1;
     }
     state[(size_t)slot * W + c] = S;
 }
@@ -161,10 +179,53 @@ XB_EXPORT int xb_gated_scan(int out_dtype, void* y, int ldy, const float* zxg, c
 //   act = a z / rms(z) + b z^2 / rms(z^2) + c z^3 / rms(z^3) + e,   rms(v) = sqrt(mean(v^2) + eps)
 // coef = [a, b, c, e] on the device.
 // ------------------------------------------------------------------------------------------
-template <typename T>
+// Three sums over a block at once; every thread gets them.  Fixed order: lanes, then warps.
+__device__ __forceinline__ void block_sum3(float& a, float& b, float& c, float* scratch /* 3 * 32 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = (blockDim.x + 31) >> 5;
+    a = warp_sum(a); b = warp_sum(b); c = warp_sum(c);
+    if (lane == 0) { scratch[warp] = a; scratch[32 + warp] = b; scratch[64 + warp] = c; }
+    __syncthreads();
+    a = warp_sum(lane < nwarps ? scratch[lane] : 0.f);
+    b = warp_sum(lane < nwarps ? scratch[32 + lane] : 0.f);
+    c = warp_sum(lane < nwarps ? scratch[64 + lane] : 0.f);
+}
+
+// PER values of the row per thread stay in registers between the sums and the result (F <= PER * threads).
+template <typename T, int PER>
 __global__ void polynorm_kernel(T* __restrict__ out, const float* __restrict__ z, const float* __restrict__ coef, int F,
                                 float eps) {
-    __shared__ float scratch[33];
+    __shared__ float scratch[96];
+    const float* zr = z + (size_t)blockIdx.x * F;
+    float v[PER];
+    float s2 = 0.f, s4 = 0.f, s6 = 0.f;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        v[k] = i < F ? zr[i] : 0.f;
+        const float v2 = v[k] * v[k];
+        s2 += v2;
+        s4 += v2 * v2;
+        s6 += v2 * v2 * v2;
+    }
+    block_sum3(s2, s4, s6, scratch);
+    const float r1 = coef[0] / sqrtf(s2 / (float)F + eps);
+    const float r2 = coef[1] / sqrtf(s4 / (float)F + eps);
+    const float r3 = coef[2] / sqrtf(s6 / (float)F + eps);
+    const float e = coef[3];
+    T* o = out + (size_t)blockIdx.x * F;
+#pragma unroll
+    for (int k = 0; k < PER; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        const float v2 = v[k] * v[k];
+        if (i < F) o[i] = from_f32<T>(v[k] * r1 + v2 * r2 + v2 * v[k] * r3 + e);
+    }
+}
+
+// rows longer than 16 values per thread of the largest block: two passes over the row
+template <typename T>
+__global__ void polynorm_long_kernel(T* __restrict__ out, const float* __restrict__ z, const float* __restrict__ coef, int F,
+                                     float eps) {
+    __shared__ float scratch[96];
     const float* zr = z + (size_t)blockIdx.x * F;
     float s2 = 0.f, s4 = 0.f, s6 = 0.f;
     for (int i = threadIdx.x; i < F; i += blockDim.x) {
@@ -173,9 +234,7 @@ __global__ void polynorm_kernel(T* __restrict__ out, const float* __restrict__ z
         s4 += v2 * v2;
         s6 += v2 * v2 * v2;
     }
-    s2 = block_sum(s2, scratch);
-    s4 = block_sum(s4, scratch);
-    s6 = block_sum(s6, scratch);
+    block_sum3(s2, s4, s6, scratch);
     const float r1 = coef[0] / sqrtf(s2 / (float)F + eps);
     const float r2 = coef[1] / sqrtf(s4 / (float)F + eps);
     const float r3 = coef[2] / sqrtf(s6 / (float)F + eps);
@@ -187,13 +246,18 @@ __global__ void polynorm_kernel(T* __restrict__ out, const float* __restrict__ z
     }
 }
 
+template <typename T>
+static int polynorm_launch(void* out, const float* z, const float* coef, int rows, int F, float eps, cudaStream_t stream) {
+    if (F <= 4 * 256) polynorm_kernel<T, 4><<<rows, (F + 3) / 4 < 32 ? 32 : ((F + 3) / 4 + 31) / 32 * 32, 0, stream>>>((T*)out, z, coef, F, eps);
+    else if (F <= 8 * 512) polynorm_kernel<T, 8><<<rows, ((F + 7) / 8 + 31) / 32 * 32, 0, stream>>>((T*)out, z, coef, F, eps);
+    else if (F <= 16 * 1024) polynorm_kernel<T, 16><<<rows, ((F + 15) / 16 + 31) / 32 * 32, 0, stream>>>((T*)out, z, coef, F, eps);
+    else polynorm_long_kernel<T><<<rows, 1024, 0, stream>>>((T*)out, z, coef, F, eps);
+    return xb_launch_status();
+}
+
 XB_EXPORT int xb_polynorm(int out_dtype, void* out, const float* z, const float* coef, int rows, int F, float eps,
                           cudaStream_t stream) {
     if (rows <= 0) return 0;
-    const int threads = F >= 2048 ? 512 : 256;
-    if (out_dtype == XB_F32)
-        polynorm_kernel<float><<<rows, threads, 0, stream>>>((float*)out, z, coef, F, eps);
-    else
-        polynorm_kernel<__nv_bfloat16><<<rows, threads, 0, stream>>>((__nv_bfloat16*)out, z, coef, F, eps);
-    return xb_launch_status();
+    if (out_dtype == XB_F32) return polynorm_launch<float>(out, z, coef, rows, F, eps, stream);
+    return polynorm_launch<__nv_bfloat16>(out, z, coef, rows, F, eps, stream);
 }

@@ -20,9 +20,12 @@
 
 using namespace xbmma;
 
+__device__ __forceinline__ void cp_async_wait_but_one() { asm volatile("cp.async.wait_group 1;\n" ::: "memory"); }
+
 constexpr int TM_THREADS = 256;
 constexpr int TM_WARPS = 8;
 constexpr int TM_BK = 32;
+constexpr int TM_LDS = TM_BK + 1;    // a score row's stride in shared memory: rows of one query tile fall into different banks
 
 struct TalkMmaArgs {
     const int* q_start;
@@ -52,7 +55,8 @@ __host__ __device__ inline TalkMmaSmem talk_mma_smem(int H, int G, int d, int dv
     L.v = at; at += (size_t)G * TM_BK * L.ldv * 2;
     L.p = at; at += (size_t)G * L.rows * L.ldp * 2;
     at = (at + 15) / 16 * 16;
-    L.s = at; at += (size_t)H * bq * TM_BK * 4;
+    L.s = at; at += (size_t)H * bq * TM_LDS * 4;
+    at = (at + 15) / 16 * 16;      // the mix matrix is read in 16-byte pieces
     L.talk = at; at += (size_t)maxh * maxh * 4;
     L.rm = at; at += (size_t)H * bq * 4;
     L.rl = at; at += (size_t)H * bq * 4;
@@ -146,31 +150,50 @@ __global__ void __launch_bounds__(TM_THREADS) attn_talking_mma_kernel(__nv_bfloa
         hi = min(hi, first + per * TM_BK);
     }
     const int vch = dv / 8;
-    for (int k0 = lo / TM_BK * TM_BK; k0 < hi; k0 += TM_BK) {
-        __syncthreads();                                    // the tile before is done with Ks, Vs, S, Pb
-        // a. keys and values of all kv heads
-        for (int e = tid; e < G * TM_BK * (dch + vch); e += TM_THREADS) {
-            const int per_key = dch + vch;
-            const int c = e % per_key, j = (e / per_key) % TM_BK, g = e / (per_key * TM_BK);
-            const int key = k0 + j;
-            const void* src = k_cache;
-            int bytes = 0;
+    __shared__ int rowbase[2][TM_BK];          // per key of a tile: its row in the cache for kv head 0, or -1 ([0]: keys, [1]: values)
+    const int bq_shift = 31 - __clz(BQ);       // BQ is a power of two
+
+    // Rows of one tile are fetched by warps: a warp takes (kv head, key) rows in turn, its lanes the row's
+    // 16-byte pieces.  Where the rows lie is worked out once per tile by 32 threads.
+    auto find_rows = [&](int k0, int which) {
+        if (tid < TM_BK) {
+            const int key = k0 + tid;
+            int rb = -1;
             if (key >= lo && key < hi) {
                 const int page = table[key / a.page_size];
-                if (page < 0 || page >= a.num_pages) {
-                    if (c == 0) atomicOr(a.err, XB_ERR_BAD_PAGE);
-                } else {
-                    const size_t rowi = ((size_t)page * G + g) * a.page_size + key % a.page_size;
-                    src = c < dch ? (const void*)(k_cache + rowi * d + c * 8) : (const void*)(v_cache + rowi * dv + (c - dch) * 8);
-                    bytes = 16;
-                }
+                if (page < 0 || page >= a.num_pages) atomicOr(a.err, XB_ERR_BAD_PAGE);
+                else rb = page * G * a.page_size + key % a.page_size;
             }
-            const uint32_t dst = c < dch ? smem_addr(Ks + ((size_t)g * TM_BK + j) * L.ldk + c * 8)
-                                         : smem_addr(Vs + ((size_t)g * TM_BK + j) * L.ldv + (c - dch) * 8);
-            cp_async16(dst, src, bytes);
+            rowbase[which][tid] = rb;
+        }
+    };
+    // a warp's lanes take the 16-byte pieces of one row, or of two rows at once where a row has at most 16 pieces
+    auto fetch = [&](const __nv_bfloat16* cache, __nv_bfloat16* tile, const int* rows, int width, int ld, int pieces) {
+        const int two = pieces <= 16 ? 1 : 0;
+        const int sub = two ? lane >> 4 : 0, c0 = two ? lane & 15 : lane, step = two ? 16 : 32;
+        for (int it = (warp << two) + sub; it < G * TM_BK; it += TM_WARPS << two) {
+            const int g = it / TM_BK, j = it % TM_BK;
+            const int rb = rows[j];
+            const __nv_bfloat16* src = cache + (rb >= 0 ? ((size_t)rb + (size_t)g * a.page_size) * width : 0);
+            const uint32_t dst = smem_addr(tile + ((size_t)g * TM_BK + j) * ld);
+            for (int c = c0; c < pieces; c += step) cp_async16(dst + c * 16, rb >= 0 ? src + c * 8 : src, rb >= 0 ? 16 : 0);
         }
         cp_async_commit();
-        cp_async_wait_all();
+    };
+    auto fetch_keys = [&](void) { fetch(k_cache, Ks, rowbase[0], d, L.ldk, dch); };
+    auto fetch_values = [&](void) { fetch(v_cache, Vs, rowbase[1], dv, L.ldv, vch); };
+    const int k_first = lo / TM_BK * TM_BK;
+    __syncthreads();                                        // the queries, the mix matrix and the rows' start values are in place
+    if (k_first < hi) {
+        find_rows(k_first, 0);
+        find_rows(k_first, 1);
+        __syncthreads();
+        fetch_keys();
+        fetch_values();
+    }
+    for (int k0 = k_first; k0 < hi; k0 += TM_BK) {
+        // a. this tile's keys have been asked for (and its values behind them): wait for the keys
+        cp_async_wait_but_one();
         __syncthreads();
         // b. raw scores per unit
         for (int u = warp; u < units; u += TM_WARPS) {
@@ -200,54 +223,57 @@ __global__ void __launch_bounds__(TM_THREADS) attn_talking_mma_kernel(__nv_bfloa
                     const int r = mt * 16 + (lane >> 2) + (c >> 1) * 8;
                     const int j = n * 8 + (lane & 3) * 2 + (c & 1);
                     if (r < R) {
-                        const int hl = r / BQ, i = r - hl * BQ;
-                        S[((size_t)(g * rep + hl) * BQ + i) * TM_BK + j] = acc[n][c] * a.scale;
+                        const int hl = r >> bq_shift, i = r & (BQ - 1);
+                        S[((size_t)(g * rep + hl) * BQ + i) * TM_LDS + j] = acc[n][c] * a.scale;
                     }
                 }
         }
-        __syncthreads();
-        // c. mix across heads and mask: one thread per (query, key)
-        for (int e = tid; e < BQ * TM_BK; e += TM_THREADS) {
-            const int j = e % TM_BK, i = e / TM_BK;
-            const int key = k0 + j, p = p0 + i;
-            const bool seen = i < nq && key >= lo && key < hi && key <= p && (a.window <= 0 || key > p - a.window);
-            float s[MAXH];
+        if (k0 + TM_BK < hi) find_rows(k0 + TM_BK, 0);
+        __syncthreads();                                    // every warp is done with this tile's keys
+        if (k0 + TM_BK < hi) fetch_keys();                  // the next tile's keys arrive during the mix, the softmax and P V
+        else cp_async_commit();
+        // c + d. a warp takes one query (all heads, or an interleaved share of them where the tile has fewer
+        // queries than the block has warps), its lanes the tile's keys: every head's raw score of the pair into
+        // registers, then head by head the mix, the mask, the row's running maximum, the weights and their sum
+        {
+            const int nsplit = BQ >= TM_WARPS ? 1 : TM_WARPS / BQ;
+            for (int i = BQ >= TM_WARPS ? warp : (warp & (BQ - 1)); i < BQ; i += TM_WARPS) {
+                const int key = k0 + lane, p = p0 + i;
+                const bool seen = i < nq && key >= lo && key < hi && key <= p && (a.window <= 0 || key > p - a.window);
+                float s[MAXH];
 #pragma unroll
-            for (int g = 0; g < MAXH; ++g) s[g] = g < H ? S[((size_t)g * BQ + i) * TM_BK + j] : 0.f;
+                for (int g = 0; g < MAXH; ++g) s[g] = g < H ? S[((size_t)g * BQ + i) * TM_LDS + lane] : 0.f;
 #pragma unroll 1
-            for (int h = 0; h < H; ++h) {
-                const float4* tr = reinterpret_cast<const float4*>(tk + h * MAXH);
-                float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
+                for (int h = BQ >= TM_WARPS ? 0 : (warp >> bq_shift); h < H; h += nsplit) {
+                    const float4* tr = reinterpret_cast<const float4*>(tk + h * MAXH);
+                    float m0 = 0.f, m1 = 0.f, m2 = 0.f, m3 = 0.f;
 #pragma unroll
-                for (int g4 = 0; g4 < MAXH / 4; ++g4) {
-                    const float4 t = tr[g4];
-                    m0 = fmaf(t.x, s[g4 * 4], m0);
-                    m1 = fmaf(t.y, s[g4 * 4 + 1], m1);
-                    m2 = fmaf(t.z, s[g4 * 4 + 2], m2);
-                    m3 = fmaf(t.w, s[g4 * 4 + 3], m3);
+                    for (int g4 = 0; g4 < MAXH / 4; ++g4) {
+                        const float4 t = tr[g4];
+                        m0 = fmaf(t.x, s[g4 * 4], m0);
+                        m1 = fmaf(t.y, s[g4 * 4 + 1], m1);
+                        m2 = fmaf(t.z, s[g4 * 4 + 2], m2);
+                        m3 = fmaf(t.w, s[g4 * 4 + 3], m3);
+                    }
+                    const float sv = seen ? (m0 + m1) + (m2 + m3) : -INFINITY;
+                    const int r = h * BQ + i;
+                    const float m_old = rm[r];
+                    const float m_new = fmaxf(m_old, warp_max(sv));
+                    const float w = m_new == -INFINITY ? 0.f : __expf(sv - m_new);
+                    const __nv_bfloat16 wb = __float2bfloat16_rn(w);
+                    const float sum = warp_sum(__bfloat162float(wb));    // the sum of the weights as the product sees them
+                    const int g = h / rep, hl = h - g * rep;
+                    Pb[((size_t)g * L.rows + hl * BQ + i) * L.ldp + lane] = wb;
+                    __syncwarp();
+                    if (lane == 0) {
+                        rc[r] = m_new == -INFINITY ? 1.f : __expf(m_old - m_new);
+                        rl[r] = rl[r] * rc[r] + sum;
+                        rm[r] = m_new;
+                    }
                 }
-                S[((size_t)h * BQ + i) * TM_BK + j] = seen ? (m0 + m1) + (m2 + m3) : -INFINITY;
             }
         }
-        __syncthreads();
-        // d. softmax rows
-        for (int r = warp; r < H * BQ; r += TM_WARPS) {
-            const int h = r / BQ, i = r - h * BQ;
-            const float sv = S[(size_t)r * TM_BK + lane];
-            const float m_old = rm[r];
-            const float m_new = fmaxf(m_old, warp_max(sv));
-            const float w = m_new == -INFINITY ? 0.f : expf(sv - m_new);
-            const __nv_bfloat16 wb = __float2bfloat16_rn(w);
-            const float sum = warp_sum(__bfloat162float(wb));    // the sum of the weights as the product sees them
-            const int g = h / rep, hl = h - g * rep;
-            Pb[((size_t)g * L.rows + hl * BQ + i) * L.ldp + lane] = wb;
-            if (lane == 0) {
-                const float corr = m_new == -INFINITY ? 1.f : expf(m_old - m_new);
-                rc[r] = corr;
-                rl[r] = rl[r] * corr + sum;
-                rm[r] = m_new;
-            }
-        }
+        cp_async_wait_but_one();                            // this tile's values (the next keys may still be on their way)
         __syncthreads();
         // e. value sums per unit
 #pragma unroll
@@ -258,8 +284,8 @@ __global__ void __launch_bounds__(TM_THREADS) attn_talking_mma_kernel(__nv_bfloa
             float c0 = 1.f, c1 = 1.f;
             {
                 const int r0 = mt * 16 + (lane >> 2), r1 = r0 + 8;
-                if (r0 < R) c0 = rc[(g * rep + r0 / BQ) * BQ + r0 % BQ];
-                if (r1 < R) c1 = rc[(g * rep + r1 / BQ) * BQ + r1 % BQ];
+                if (r0 < R) c0 = rc[(g * rep + (r0 >> bq_shift)) * BQ + (r0 & (BQ - 1))];
+                if (r1 < R) c1 = rc[(g * rep + (r1 >> bq_shift)) * BQ + (r1 & (BQ - 1))];
             }
 #pragma unroll
             for (int n = 0; n < DVT; ++n) {
@@ -282,7 +308,12 @@ __global__ void __launch_bounds__(TM_THREADS) attn_talking_mma_kernel(__nv_bfloa
                 }
             }
         }
+        if (k0 + TM_BK < hi) find_rows(k0 + TM_BK, 1);
+        __syncthreads();                                    // every warp is done with this tile's values, weights and scores
+        if (k0 + TM_BK < hi) fetch_values();
+        else cp_async_commit();
     }
+    cp_async_wait_all();
     __syncthreads();
     // results: row r of unit (g, mt) is head g * rep + r / BQ of query r % BQ
 #pragma unroll
