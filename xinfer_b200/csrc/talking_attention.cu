@@ -341,35 +341,56 @@ __global__ void __launch_bounds__(TA_THREADS) attn_talking_kernel(T* __restrict_
     }
 }
 
-// out[t, h] = out_scale * sum_y e^(m_y - m) o_y / sum_y e^(m_y - m) l_y  over the `parts` key ranges of token t
+// out[t, h] = out_scale * sum_y e^(m_y - m) o_y / sum_y e^(m_y - m) l_y  over the `parts` key ranges of token t.
+// One block per (token, head): the ranges' factors once into shared memory, then a thread per column.
 template <typename T>
 __global__ void attn_talking_merge_kernel(T* __restrict__ out, const float* __restrict__ part_o,
                                           const float* __restrict__ part_ml, int H, int dv, int parts, int ldo,
                                           float out_scale) {
-    const int t = blockIdx.x;
-    for (int e = threadIdx.x; e < H * dv; e += blockDim.x) {
-        const int h = e / dv;
-        const float* ml = part_ml + (size_t)t * parts * H * 2 + 2 * h;
+    extern __shared__ float fy[];          // [parts] factors, then the sum
+    const int t = blockIdx.x, h = blockIdx.y;
+    const float* ml = part_ml + (size_t)t * parts * H * 2 + 2 * h;
+    if (threadIdx.x < 32) {
         float m = -INFINITY;
-        for (int y = 0; y < parts; ++y) m = fmaxf(m, ml[(size_t)y * H * 2]);
-        float l = 0.f, acc = 0.f;
-        for (int y = 0; y < parts; ++y) {
+        for (int y = threadIdx.x; y < parts; y += 32) m = fmaxf(m, ml[(size_t)y * H * 2]);
+        m = warp_max(m);
+        float l = 0.f;
+        for (int y = threadIdx.x; y < parts; y += 32) {
             const float my = ml[(size_t)y * H * 2];
-            if (my == -INFINITY) continue;
-            const float f = expf(my - m);
+            const float f = my == -INFINITY ? 0.f : expf(my - m);
+            fy[y] = f;
             l += f * ml[(size_t)y * H * 2 + 1];
-            acc += f * part_o[((size_t)t * parts + y) * H * dv + e];
         }
-        out[(size_t)t * ldo + e] = from_f32<T>(l > 0.f ? acc / l * out_scale : 0.f);
+        l = warp_sum(l);
+        if (threadIdx.x == 0) fy[parts] = l;
     }
+    __syncthreads();
+    const float l = fy[parts];
+    const float scale = l > 0.f ? out_scale / l : 0.f;
+    for (int c = threadIdx.x; c < dv; c += blockDim.x) {
+        float acc = 0.f;
+        for (int y = 0; y < parts; ++y) {
+            const float f = fy[y];
+            if (f != 0.f) acc = fmaf(f, part_o[(((size_t)t * parts + y) * H + h) * dv + c], acc);
+        }
+        out[(size_t)t * ldo + (size_t)h * dv + c] = from_f32<T>(acc * scale);
+    }
+}
+
+template <typename T>
+static int talking_merge_launch(void* out, const float* part_o, const float* part_ml, int tokens, int H, int dv, int parts,
+                                int ldo, float out_scale, cudaStream_t stream) {
+    const int threads = dv >= 128 ? 128 : (dv >= 64 ? 64 : 32);
+    attn_talking_merge_kernel<T><<<dim3(tokens, H), threads, (parts + 1) * sizeof(float), stream>>>((T*)out, part_o, part_ml, H, dv,
+                                                                                                  parts, ldo, out_scale);
+    return xb_launch_status();
 }
 
 // the merge alone, for the tensor-core form of the kernel (talking_attention_mma.cu)
 extern "C" int xb_attn_talking_merge_bf16(void* out, const float* part_o, const float* part_ml, int tokens, int H, int dv,
                                           int parts, int ldo, float out_scale, cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    attn_talking_merge_kernel<__nv_bfloat16><<<tokens, 128, 0, stream>>>((__nv_bfloat16*)out, part_o, part_ml, H, dv, parts, ldo, out_scale);
-    return xb_launch_status();
+    return talking_merge_launch<__nv_bfloat16>(out, part_o, part_ml, tokens, H, dv, parts, ldo, out_scale, stream);
 }
 
 static size_t talking_smem(int H, int d, int dv, int bq) {
@@ -411,8 +432,7 @@ XB_EXPORT int xb_attn_talking(int dtype, void* out, int ldo, const void* q, cons
                                                                       (const float*)v_cache, a);
         rc = xb_launch_status();
         if (rc == 0 && a.parts > 1) {
-            attn_talking_merge_kernel<float><<<tokens, 128, 0, stream>>>((float*)out, part_o, part_ml, nh, dv, a.parts, ldo, out_scale);
-            rc = xb_launch_status();
+            rc = talking_merge_launch<float>(out, part_o, part_ml, tokens, nh, dv, a.parts, ldo, out_scale, stream);
         }
     } else {
         typedef __nv_bfloat16 bf;
@@ -421,8 +441,7 @@ XB_EXPORT int xb_attn_talking(int dtype, void* out, int ldo, const void* q, cons
                                                                    (const bf*)v_cache, a);
         rc = xb_launch_status();
         if (rc == 0 && a.parts > 1) {
-            attn_talking_merge_kernel<bf><<<tokens, 128, 0, stream>>>((bf*)out, part_o, part_ml, nh, dv, a.parts, ldo, out_scale);
-            rc = xb_launch_status();
+            rc = talking_merge_launch<bf>(out, part_o, part_ml, tokens, nh, dv, a.parts, ldo, out_scale, stream);
         }
     }
     return rc;

@@ -171,12 +171,17 @@ __global__ void __launch_bounds__(TM_THREADS) attn_talking_mma_kernel(__nv_bfloa
     auto fetch = [&](const __nv_bfloat16* cache, __nv_bfloat16* tile, const int* rows, int width, int ld, int pieces) {
         const int two = pieces <= 16 ? 1 : 0;
         const int sub = two ? lane >> 4 : 0, c0 = two ? lane & 15 : lane, step = two ? 16 : 32;
-        for (int it = (warp << two) + sub; it < G * TM_BK; it += TM_WARPS << two) {
-            const int g = it / TM_BK, j = it % TM_BK;
+        const int per_pass = TM_WARPS << two;                 // rows the block's warps take at once
+        // a thread meets the same few keys for every kv head: their rows are looked up once, the heads are strides
+        for (int j = (warp << two) + sub; j < TM_BK; j += per_pass) {
             const int rb = rows[j];
-            const __nv_bfloat16* src = cache + (rb >= 0 ? ((size_t)rb + (size_t)g * a.page_size) * width : 0);
-            const uint32_t dst = smem_addr(tile + ((size_t)g * TM_BK + j) * ld);
-            for (int c = c0; c < pieces; c += step) cp_async16(dst + c * 16, rb >= 0 ? src + c * 8 : src, rb >= 0 ? 16 : 0);
+            const bool ok = rb >= 0;
+            const __nv_bfloat16* src = cache + (ok ? (size_t)rb * width : 0);
+            const size_t src_step = ok ? (size_t)a.page_size * width : 0;
+            uint32_t dst = smem_addr(tile + (size_t)j * ld);
+            const uint32_t dst_step = (uint32_t)(TM_BK * ld * 2);
+            for (int g = 0; g < G; ++g, src += src_step, dst += dst_step)
+                for (int c = c0; c < pieces; c += step) cp_async16(dst + c * 16, src + c * 8, ok ? 16 : 0);
         }
         cp_async_commit();
     };
