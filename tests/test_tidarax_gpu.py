@@ -405,12 +405,16 @@ def test_polynorm_equals_plain(out_dtype):
 # ---------------------------------------------------------------------------------------------
 # experts by table
 # ---------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("dtype,tensor_cores", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
+@pytest.mark.parametrize("dtype,tensor_cores,dense_up_to", [(torch.float32, False, 32), (torch.bfloat16, False, 0),
+                                                            (torch.bfloat16, True, 0), (torch.bfloat16, True, 32)])
 @pytest.mark.parametrize("E,top,ff,hid,T", [(5, 2, 24, 48, 77), (8, 1, 40, 64, 3), (3, 3, 16, 32, 130), (16, 4, 72, 96, 1),
                                             (4, 2, 200, 136, 300), (2, 1, 60, 44, 9)])
-def test_table_experts_equal_plain(dtype, tensor_cores, E, top, ff, hid, T, monkeypatch):
+def test_table_experts_equal_plain(dtype, tensor_cores, dense_up_to, E, top, ff, hid, T, monkeypatch):
+    """The grouped form on FMA units and on tensor cores, and the dense form that steps of few tokens take."""
     from xinfer_b200.config.plan import ExpertTableSpec
+    from xinfer_b200.parts import table_experts
     monkeypatch.setattr(_k(), "expert_tensor_cores", tensor_cores)
+    monkeypatch.setattr(table_experts, "DENSE_MAX_TOKENS", dense_up_to)
     from xinfer_b200.parts import StepContext, Workspace, build_part
     vocab = 41
     g = torch.Generator().manual_seed(E * 10 + top)
@@ -457,8 +461,11 @@ def test_table_experts_equal_plain(dtype, tensor_cores, E, top, ff, hid, T, monk
                            token_ids=_i32([int(ids[t])]), positions=_i32([0]), req_of_token=_i32([0]), q_start=_i32([0, 1]),
                            start_pos=_i32([0]), slots=_i32([0]), logit_rows=_i32([0]), num_logit_rows=1, tables=[],
                            strides=[], err=err, workspace=Workspace(DEV), branch_dtype=torch.float32)
-        alone = part.forward(xd[t:t + 1].contiguous(), ctx1)
-        assert torch.equal(alone[0], out[t])
+        alone = part.forward(xd[t:t + 1].contiguous(), ctx1).clone()
+        if dtype == torch.float32 or dense_up_to == 0 or T <= dense_up_to:
+            assert torch.equal(alone[0], out[t])        # the same form took both: a row's sum has one order
+        else:                                           # one token takes the dense form, the batch the grouped one
+            assert (alone[0].double().cpu() - ref[t]).abs().max() <= tol * (1 + ref.abs().max())
 
 
 # ---------------------------------------------------------------------------------------------

@@ -87,7 +87,7 @@ XB_EXPORT int xb_expert_route(int* offsets, int* perm, int* inv, const int* tabl
 template <typename TA, typename TW, typename TO, bool GATED>
 __global__ void expert_gemm_kernel(TO* __restrict__ y, const TA* __restrict__ a, const TW* __restrict__ w,
                                    const int* __restrict__ offsets, const int* __restrict__ perm, int gather, int top,
-                                   int E, int N, int K) {
+                                   int E, int N, int K, long long ldw, long long estride) {
     constexpr int BM = 32, BN = 64, BK = 16;
     __shared__ float sa[BK][BM + 1];
     __shared__ float sw[GATED ? 2 : 1][BK][BN + 1];
@@ -118,7 +118,7 @@ __global__ void expert_gemm_kernel(TO* __restrict__ y, const TA* __restrict__ a,
     }
     __syncthreads();
     const int n0 = blockIdx.x * BN;
-    const TW* we = w + (size_t)e * (GATED ? 2 : 1) * N * K;
+    const TW* we = w + (size_t)e * estride;     // row n of this expert's matrix starts at we + n * ldw
     const int tx = threadIdx.x % 16, ty = threadIdx.x / 16;     // 16 x 16 threads: 4 columns x 2 rows each
     float acc[2][4], acc2[2][4];
 #pragma unroll
@@ -135,8 +135,8 @@ __global__ void expert_gemm_kernel(TO* __restrict__ y, const TA* __restrict__ a,
             const int r = idx / BK, c = idx % BK;
             const int gn = n0 + r, gk = k0 + c;
             const bool ok = gn < N && gk < K;
-            sw[0][c][r] = ok ? to_f32<TW>(we[(size_t)gn * K + gk]) : 0.f;
-            if (GATED) sw[GATED ? 1 : 0][c][r] = ok ? to_f32<TW>(we[(size_t)(N + gn) * K + gk]) : 0.f;
+            sw[0][c][r] = ok ? to_f32<TW>(we[(size_t)gn * ldw + gk]) : 0.f;
+            if (GATED) sw[GATED ? 1 : 0][c][r] = ok ? to_f32<TW>(we[(size_t)(N + gn) * ldw + gk]) : 0.f;
         }
         __syncthreads();
 #pragma unroll
@@ -179,25 +179,77 @@ __global__ void expert_gemm_kernel(TO* __restrict__ y, const TA* __restrict__ a,
 
 template <typename TA, typename TW, typename TO>
 static int expert_gemm_launch(void* y, const void* a, const void* w, const int* offsets, const int* perm, int gather, int top,
-                              int E, int rows_max, int N, int K, int gated, cudaStream_t stream) {
+                              int E, int rows_max, int N, int K, int gated, long long ldw, long long estride, cudaStream_t stream) {
     const dim3 grid((N + 63) / 64, (rows_max + 31) / 32 + E);
     if (gated)
-        expert_gemm_kernel<TA, TW, TO, true><<<grid, 256, 0, stream>>>((TO*)y, (const TA*)a, (const TW*)w, offsets, perm, gather, top, E, N, K);
+        expert_gemm_kernel<TA, TW, TO, true><<<grid, 256, 0, stream>>>((TO*)y, (const TA*)a, (const TW*)w, offsets, perm, gather, top, E, N, K, ldw, estride);
     else
-        expert_gemm_kernel<TA, TW, TO, false><<<grid, 256, 0, stream>>>((TO*)y, (const TA*)a, (const TW*)w, offsets, perm, gather, top, E, N, K);
+        expert_gemm_kernel<TA, TW, TO, false><<<grid, 256, 0, stream>>>((TO*)y, (const TA*)a, (const TW*)w, offsets, perm, gather, top, E, N, K, ldw, estride);
     return xb_launch_status();
 }
 
-// in_dtype: type of a and w; out_dtype: type of y.  rows_max: tokens * top.
+// in_dtype: type of a and w; out_dtype: type of y.  rows_max: tokens * top.  Row n of expert e's matrix starts
+// at w + e * estride + n * ldw (elements): [experts, rows, K] blocks, or matrices side by side along K.
 XB_EXPORT int xb_expert_gemm(int in_dtype, int out_dtype, void* y, const void* a, const void* w, const int* offsets,
                              const int* perm, int gather, int top, int experts, int rows_max, int N, int K, int gated,
-                             cudaStream_t stream) {
+                             long long ldw, long long estride, cudaStream_t stream) {
     if (rows_max <= 0 || N <= 0) return 0;
     typedef __nv_bfloat16 bf;
-#define XB_ARGS y, a, w, offsets, perm, gather, top, experts, rows_max, N, K, gated, stream
+#define XB_ARGS y, a, w, offsets, perm, gather, top, experts, rows_max, N, K, gated, ldw, estride, stream
     if (in_dtype == XB_F32) return out_dtype == XB_F32 ? expert_gemm_launch<float, float, float>(XB_ARGS) : (int)cudaErrorInvalidValue;
     return out_dtype == XB_F32 ? expert_gemm_launch<bf, bf, float>(XB_ARGS) : expert_gemm_launch<bf, bf, bf>(XB_ARGS);
 #undef XB_ARGS
+}
+
+// ------------------------------------------------------------------------------------------
+// For steps of few tokens: every expert's gate/up values of every token come from ONE dense product with the
+// experts' matrices stacked (weights are read once, as they would be anyway once most experts are in use).
+//   act[t, e * F + f] = weight * silu(gu[t, e*2F + f]) * gu[t, e*2F + F + f]   if e is one of token t's experts
+//                     = 0                                                       otherwise
+// so that ONE product with the down matrices side by side along K sums the token's experts.
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void expert_select_gate_kernel(T* __restrict__ act, const T* __restrict__ gu, const int* __restrict__ table,
+                                          const int* __restrict__ ids, const int* __restrict__ sampled, int num_sampled,
+                                          const int* __restrict__ req_of_token, int top, int E, int F, int vocab,
+                                          float weight, int* err) {
+    const int t = blockIdx.x, e = blockIdx.y;
+    int id = ids[t];
+    if (id < 0 && sampled != nullptr && -1 - id < num_sampled) id = sampled[-1 - id];
+    bool chosen = false;
+    if (req_of_token[t] >= 0) {
+        if (id < 0 || id >= vocab) {
+            if (threadIdx.x == 0 && e == 0) atomicOr(err, XB_ERR_BAD_TOKEN);
+        } else {
+            for (int k = 0; k < top; ++k) chosen |= table[(size_t)id * top + k] == e;
+        }
+    }
+    const T* g = gu + ((size_t)t * E + e) * 2 * F;
+    T* o = act + ((size_t)t * E + e) * F;
+    for (int f = threadIdx.x; f < F; f += blockDim.x) {
+        float v = 0.f;
+        if (chosen) {
+            const float a = to_f32<T>(g[f]), u = to_f32<T>(g[F + f]);
+            v = a / (1.f + expf(-a)) * u * weight;
+        }
+        o[f] = from_f32<T>(v);
+    }
+}
+
+XB_EXPORT int xb_expert_select_gate(int dtype, void* act, const void* gu, const int* table, const int* ids, const int* sampled,
+                                    int num_sampled, const int* req_of_token, int tokens, int top, int experts, int F, int vocab,
+                                    int* err, cudaStream_t stream) {
+    if (tokens <= 0) return 0;
+    const dim3 grid(tokens, experts);
+    const float weight = 1.f / (float)top;
+    if (dtype == XB_F32)
+        expert_select_gate_kernel<float><<<grid, 256, 0, stream>>>((float*)act, (const float*)gu, table, ids, sampled, num_sampled,
+                                                                   req_of_token, top, experts, F, vocab, weight, err);
+    else
+        expert_select_gate_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>((__nv_bfloat16*)act, (const __nv_bfloat16*)gu, table, ids,
+                                                                           sampled, num_sampled, req_of_token, top, experts, F,
+                                                                           vocab, weight, err);
+    return xb_launch_status();
 }
 
 // ------------------------------------------------------------------------------------------

@@ -19,7 +19,7 @@ __global__ void __launch_bounds__(EG_THREADS) expert_gemm_mma_kernel(TO* __restr
                                                                      const __nv_bfloat16* __restrict__ w,
                                                                      const int* __restrict__ offsets,
                                                                      const int* __restrict__ perm, int gather, int top, int E,
-                                                                     int N, int K) {
+                                                                     int N, int K, long long ldw, long long estride) {
     extern __shared__ __align__(16) unsigned char eg_smem[];
     typedef __nv_bfloat16 (*Tile)[EG_BM][EG_LD];            // EG_BM == EG_BN
     Tile As = reinterpret_cast<Tile>(eg_smem);
@@ -50,7 +50,7 @@ __global__ void __launch_bounds__(EG_THREADS) expert_gemm_mma_kernel(TO* __restr
     __syncthreads();
     constexpr int COLS = GATED ? EG_BN / 2 : EG_BN;           // output columns of a block
     const int n0 = blockIdx.x * COLS;
-    const __nv_bfloat16* we = w + (size_t)e * (GATED ? 2 : 1) * N * K;
+    const __nv_bfloat16* we = w + (size_t)e * estride;       // row n of this expert's matrix starts at we + n * ldw
     const int wm = warp >> 1, wn = warp & 1;                  // 4 x 2 warps: 32 rows x 64 matrix rows each
 
     auto load = [&](int stage, int k0) {
@@ -67,7 +67,7 @@ __global__ void __launch_bounds__(EG_THREADS) expert_gemm_mma_kernel(TO* __restr
                 // gated: matrix rows 0..63 are gate columns n0.., rows 64..127 the same columns of up
                 const int gn = GATED ? (br < 64 ? n0 + br : N + n0 + (br - 64)) : n0 + br;
                 const bool ok = (GATED ? (n0 + (br & 63)) < N : gn < N) && gk < K;
-                cp_async16(smem_addr(&Bs[stage][br][c]), ok ? (const void*)(we + (size_t)gn * K + gk) : (const void*)w, ok ? 16 : 0);
+                cp_async16(smem_addr(&Bs[stage][br][c]), ok ? (const void*)(we + (size_t)gn * ldw + gk) : (const void*)w, ok ? 16 : 0);
             }
         }
         cp_async_commit();
@@ -140,9 +140,10 @@ __global__ void __launch_bounds__(EG_THREADS) expert_gemm_mma_kernel(TO* __restr
 
 // bfloat16 operands, K a multiple of 8 (16-byte copies); returns cudaErrorNotSupported for other sizes.
 XB_EXPORT int xb_expert_gemm_mma(int out_dtype, void* y, const void* a, const void* w, const int* offsets, const int* perm,
-                                 int gather, int top, int experts, int rows_max, int N, int K, int gated, cudaStream_t stream) {
+                                 int gather, int top, int experts, int rows_max, int N, int K, int gated, long long ldw,
+                                 long long estride, cudaStream_t stream) {
     if (rows_max <= 0 || N <= 0) return 0;
-    if (K % 8 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorNotSupported;
+    if (K % 8 || ldw % 8 || estride % 8 || ((uintptr_t)a & 15) || ((uintptr_t)w & 15)) return (int)cudaErrorNotSupported;
     typedef __nv_bfloat16 bf;
     const int cols = gated ? EG_BN / 2 : EG_BN;
     const dim3 grid((N + cols - 1) / cols, (rows_max + EG_BM - 1) / EG_BM + experts);
@@ -150,7 +151,7 @@ XB_EXPORT int xb_expert_gemm_mma(int out_dtype, void* y, const void* a, const vo
     do {                                                                                                                      \
         cudaFuncSetAttribute(expert_gemm_mma_kernel<TO, G>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)EG_SMEM);       \
         expert_gemm_mma_kernel<TO, G><<<grid, EG_THREADS, EG_SMEM, stream>>>((TO*)y, (const bf*)a, (const bf*)w, offsets, perm, \
-                                                                            gather, top, experts, N, K);                      \
+                                                                            gather, top, experts, N, K, ldw, estride);        \
     } while (0)
     if (out_dtype == XB_F32) {
         if (gated) XB_EG(float, true); else XB_EG(float, false);

@@ -752,26 +752,49 @@ def expert_route(offsets, perm, inv, table, ids, sampled, req_of_token, tokens, 
 expert_tensor_cores = True
 
 
-def expert_gemm(y, a, w, offsets, perm, gather: bool, top: int, gated: bool):
-    """y[r] = a[src(r)] . w[e(r)]^T over rows grouped by expert (``expert_route``); ``w`` is
-    ``[experts, N, K]`` (``[experts, 2 N, K]`` when ``gated``: y = silu(gate) * up)."""
-    E = w.shape[0]
-    N = w.shape[1] // (2 if gated else 1)
-    K = w.shape[2]
+def expert_gemm(y, a, w, offsets, perm, gather: bool, top: int, gated: bool, *, side_by_side: bool = False):
+    """y[r] = a[src(r)] . w[e(r)]^T over rows grouped by expert (``expert_route``).  ``w`` is
+    ``[experts, N, K]`` (``[experts, 2 N, K]`` when ``gated``: y = silu(gate) * up), or with
+    ``side_by_side`` ``[N, experts * K]``: the experts' matrices beside each other along K."""
     rows = y.shape[0]
-    _need(w, "w", a.dtype, (E, None, K))
+    if side_by_side:
+        E = offsets.numel() - 1
+        N, K = w.shape[0], w.shape[1] // E
+        _need(w, "w", a.dtype, (N, E * K))
+        ldw, estride = E * K, K
+    else:
+        E = w.shape[0]
+        N = w.shape[1] // (2 if gated else 1)
+        K = w.shape[2]
+        _need(w, "w", a.dtype, (E, None, K))
+        ldw, estride = K, w.shape[1] * K
     _need(a, "a", None, (None, K))
     _need(y, "y", None, (rows, N))
     if expert_tensor_cores and a.dtype == torch.bfloat16 and K % 8 == 0:
         rc = kernels_lib().xb_expert_gemm_mma(dtype_code(y.dtype), y.data_ptr(), a.data_ptr(), w.data_ptr(), offsets.data_ptr(),
                                               perm.data_ptr(), int(bool(gather)), int(top), E, rows, N, K, int(bool(gated)),
-                                              _stream())
+                                              ldw, estride, _stream())
         if rc != ERR_NOT_SUPPORTED:
             _ok(rc, "expert_gemm_mma")
             return
     _ok(kernels_lib().xb_expert_gemm(dtype_code(a.dtype), dtype_code(y.dtype), y.data_ptr(), a.data_ptr(), w.data_ptr(),
                                      offsets.data_ptr(), perm.data_ptr(), int(bool(gather)), int(top), E, rows, N, K,
-                                     int(bool(gated)), _stream()), "expert_gemm")
+                                     int(bool(gated)), ldw, estride, _stream()), "expert_gemm")
+
+
+def expert_select_gate(act, gu, table, ids, sampled, req_of_token, top: int, experts: int, err):
+    """From every expert's gate/up values of every token, ``gu [T, experts * 2 F]``, the inputs of the down
+    product with the experts side by side: ``act [T, experts * F]`` holds ``silu(gate) * up / top`` for a
+    token's own experts and zero for the others."""
+    T = gu.shape[0]
+    Fdim = gu.shape[1] // (2 * experts)
+    _need(gu, "gu", None, (T, experts * 2 * Fdim))
+    _need(act, "act", gu.dtype, (T, experts * Fdim))
+    _need(table, "table", torch.int32, (None, top))
+    _ok(kernels_lib().xb_expert_select_gate(dtype_code(gu.dtype), act.data_ptr(), gu.data_ptr(), table.data_ptr(), ids.data_ptr(),
+                                            _ptr(sampled), sampled.numel() if sampled is not None else 0,
+                                            req_of_token.data_ptr(), T, int(top), int(experts), Fdim, table.shape[0],
+                                            err.data_ptr(), _stream()), "expert_select_gate")
 
 
 def expert_combine(out, y, inv, top: int):

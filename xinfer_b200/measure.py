@@ -436,7 +436,7 @@ def tidarax_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, h
     E, F = experts, expert_ff
     rows = tokens * top
     x = bf(tokens, hidden)
-    wgu, wd = bf(E, 2 * F, hidden) * 0.02, bf(E, hidden, F) * 0.02
+    wgu, wd = bf(E, 2 * F, hidden) * 0.02, bf(hidden, E * F) * 0.02
     table = torch.rand(1000, E, device=device).argsort(dim=1)[:, :top].to(torch.int32).contiguous()
     ids = torch.randint(0, 1000, (tokens,), device=device, dtype=torch.int32)
     offsets = torch.zeros(E + 1, dtype=torch.int32, device=device)
@@ -444,7 +444,7 @@ def tidarax_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, h
     kernels.expert_route(offsets, perm, inv_, table, ids, None, req, tokens, top, E, err)
     act, y = torch.empty(rows, F, dtype=torch.bfloat16, device=device), torch.empty(rows, hidden, device=device)
     us1 = _loop_time_us(lambda: kernels.expert_gemm(act, x, wgu, offsets, perm, True, top, True))
-    us2 = _loop_time_us(lambda: kernels.expert_gemm(y, act, wd, offsets, perm, False, top, False))
+    us2 = _loop_time_us(lambda: kernels.expert_gemm(y, act, wd, offsets, perm, False, top, False, side_by_side=True))
     us0 = _loop_time_us(lambda: kernels.expert_route(offsets, perm, inv_, table, ids, None, req, tokens, top, E, err))
     f1, f2 = 2.0 * rows * 2 * F * hidden, 2.0 * rows * hidden * F
     for name, us, fl in (("experts: gate/up product with the gate (mma.sync)", us1, f1), ("experts: down product (mma.sync)", us2, f2)):
