@@ -405,16 +405,20 @@ def test_polynorm_equals_plain(out_dtype):
 # ---------------------------------------------------------------------------------------------
 # experts by table
 # ---------------------------------------------------------------------------------------------
-@pytest.mark.parametrize("dtype,tensor_cores,dense_up_to", [(torch.float32, False, 32), (torch.bfloat16, False, 0),
-                                                            (torch.bfloat16, True, 0), (torch.bfloat16, True, 32)])
+@pytest.mark.parametrize("dtype,tensor_cores,dense_up_to,library", [
+    (torch.float32, False, 32, False), (torch.bfloat16, False, 0, False), (torch.bfloat16, True, 0, False),
+    (torch.bfloat16, True, 32, False), (torch.bfloat16, True, 32, True), (torch.bfloat16, True, 0, True)])
 @pytest.mark.parametrize("E,top,ff,hid,T", [(5, 2, 24, 48, 77), (8, 1, 40, 64, 3), (3, 3, 16, 32, 130), (16, 4, 72, 96, 1),
                                             (4, 2, 200, 136, 300), (2, 1, 60, 44, 9)])
-def test_table_experts_equal_plain(dtype, tensor_cores, dense_up_to, E, top, ff, hid, T, monkeypatch):
-    """The grouped form on FMA units and on tensor cores, and the dense form that steps of few tokens take."""
+def test_table_experts_equal_plain(dtype, tensor_cores, dense_up_to, library, E, top, ff, hid, T, monkeypatch):
+    """The grouped form on FMA units and on tensor cores, the dense form that steps of few tokens take, and the
+    form that gives each expert's rows to the library's product when the host knows the ids."""
     from xinfer_b200.config.plan import ExpertTableSpec
     from xinfer_b200.parts import table_experts
     monkeypatch.setattr(_k(), "expert_tensor_cores", tensor_cores)
     monkeypatch.setattr(table_experts, "DENSE_MAX_TOKENS", dense_up_to)
+    monkeypatch.setattr(table_experts, "PER_EXPERT_LIBRARY_PRODUCTS", library)
+    monkeypatch.setattr(table_experts, "LIBRARY_FROM_FLOP_PER_CALL", 0.0)     # the test's sizes are tiny
     from xinfer_b200.parts import StepContext, Workspace, build_part
     vocab = 41
     g = torch.Generator().manual_seed(E * 10 + top)
@@ -438,7 +442,8 @@ def test_table_experts_equal_plain(dtype, tensor_cores, dense_up_to, E, top, ff,
     ids = torch.randint(0, vocab, (T,), generator=g)
     ids_dev = ids.to(torch.int32)
     sampled = _i32([int(ids[0]), 5])
-    ids_dev[0] = -1                                   # the first token's id waits on the device
+    if not library:
+        ids_dev[0] = -1                               # the first token's id waits on the device
     x = (torch.randn(T, hid, generator=g)).to(dtype)
     pad = 2                                           # two padding rows at the end
     xd = torch.cat([x, torch.zeros(pad, hid, dtype=dtype)]).to(DEV)
@@ -448,7 +453,14 @@ def test_table_experts_equal_plain(dtype, tensor_cores, dense_up_to, E, top, ff,
     ctx = StepContext(dtype=dtype, device=torch.device(DEV), num_tokens=T + pad, num_entries=1, token_ids=tok,
                       positions=tok, req_of_token=req, q_start=_i32([0, T]), start_pos=_i32([0]), slots=_i32([0]),
                       logit_rows=_i32([0]), num_logit_rows=1, tables=[], strides=[], err=err, workspace=Workspace(DEV),
-                      sampled=sampled, branch_dtype=torch.float32)
+                      sampled=sampled, branch_dtype=torch.float32, real_tokens=T + pad,
+                      h_token_ids=np.concatenate([ids_dev.numpy(), np.zeros(pad, dtype=np.int32)]))
+    if library:     # the library form wants a step without padding rows
+        xd, req, tok = xd[:T].contiguous(), req[:T].contiguous(), tok[:T].contiguous()
+        ctx = StepContext(dtype=dtype, device=torch.device(DEV), num_tokens=T, num_entries=1, token_ids=tok, positions=tok,
+                          req_of_token=req, q_start=_i32([0, T]), start_pos=_i32([0]), slots=_i32([0]), logit_rows=_i32([0]),
+                          num_logit_rows=1, tables=[], strides=[], err=err, workspace=Workspace(DEV), sampled=sampled,
+                          branch_dtype=torch.float32, real_tokens=T, h_token_ids=ids_dev.numpy())
     out = part.forward(xd, ctx)
     assert int(err.item()) == 0 and out.dtype == torch.float32
     ref = plain.table_moe(x.double(), ids, {n: t.double() if t.is_floating_point() else t for n, t in w.items()}, "m.")
@@ -462,7 +474,7 @@ def test_table_experts_equal_plain(dtype, tensor_cores, dense_up_to, E, top, ff,
                            start_pos=_i32([0]), slots=_i32([0]), logit_rows=_i32([0]), num_logit_rows=1, tables=[],
                            strides=[], err=err, workspace=Workspace(DEV), branch_dtype=torch.float32)
         alone = part.forward(xd[t:t + 1].contiguous(), ctx1).clone()
-        if dtype == torch.float32 or dense_up_to == 0 or T <= dense_up_to:
+        if dtype == torch.float32 or (not library and (dense_up_to == 0 or T <= dense_up_to)):
             assert torch.equal(alone[0], out[t])        # the same form took both: a row's sum has one order
         else:                                           # one token takes the dense form, the batch the grouped one
             assert (alone[0].double().cpu() - ref[t]).abs().max() <= tol * (1 + ref.abs().max())

@@ -253,6 +253,36 @@ XB_EXPORT int xb_expert_select_gate(int dtype, void* act, const void* gu, const 
 }
 
 // ------------------------------------------------------------------------------------------
+// Rows in grouped order, for products that want each expert's rows as one contiguous matrix:
+//   out[r, :] = x[perm[r] / top, :]   for r < offsets[E]
+// ------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void expert_gather_kernel(T* __restrict__ out, const T* __restrict__ x, const int* __restrict__ perm,
+                                     const int* __restrict__ offsets, int top, int E, int K) {
+    const int r = blockIdx.x;
+    if (r >= offsets[E]) return;
+    const T* src = x + (size_t)(perm[r] / top) * K;
+    T* dst = out + (size_t)r * K;
+    if ((K * sizeof(T)) % 16 == 0) {
+        const int n16 = K * sizeof(T) / 16;
+        for (int i = threadIdx.x; i < n16; i += blockDim.x) reinterpret_cast<uint4*>(dst)[i] = reinterpret_cast<const uint4*>(src)[i];
+    } else {
+        for (int i = threadIdx.x; i < K; i += blockDim.x) dst[i] = src[i];
+    }
+}
+
+XB_EXPORT int xb_expert_gather(int dtype, void* out, const void* x, const int* perm, const int* offsets, int rows_max, int top,
+                               int experts, int K, cudaStream_t stream) {
+    if (rows_max <= 0) return 0;
+    if (dtype == XB_F32)
+        expert_gather_kernel<float><<<rows_max, 128, 0, stream>>>((float*)out, (const float*)x, perm, offsets, top, experts, K);
+    else
+        expert_gather_kernel<__nv_bfloat16><<<rows_max, 128, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)x, perm, offsets,
+                                                                         top, experts, K);
+    return xb_launch_status();
+}
+
+// ------------------------------------------------------------------------------------------
 // 3. combine.  out[t, :] = (1 / top) * sum_k y[inv[t * top + k], :]   (a pair without a row adds nothing)
 // ------------------------------------------------------------------------------------------
 template <typename TO>

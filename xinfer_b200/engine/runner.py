@@ -206,7 +206,7 @@ class StepAssembler:
             tables=[dev[offs[7 + g]: offs[7 + g] + Bp * offs[7 + G + g]] for g in range(G)],
             strides=[int(offs[7 + G + g]) for g in range(G)],
             err=self.err, workspace=workspace if workspace is not None else self.workspace,
-            h_q_start=host[offs[3]: offs[3] + Bp + 1].numpy().copy(), h_start_pos=starts, h_slots=slots,
+            h_q_start=host[offs[3]: offs[3] + Bp + 1].numpy().copy(), h_start_pos=starts, h_slots=slots, h_token_ids=tokens,
             real_tokens=T, real_entries=B, max_context=longest, all_single=bool((counts == 1).all()),
             fixed_shapes=into is not None, sampled=self.sampled,
         )

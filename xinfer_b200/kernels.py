@@ -797,6 +797,15 @@ def expert_select_gate(act, gu, table, ids, sampled, req_of_token, top: int, exp
                                             err.data_ptr(), _stream()), "expert_select_gate")
 
 
+def expert_gather(out, x, perm, offsets, top: int):
+    """out[r] = x[perm[r] // top] for the grouped rows r: each expert's input rows as one contiguous matrix."""
+    rows, K = out.shape
+    _need(x, "x", None, (None, K))
+    _need(out, "out", x.dtype, (rows, K))
+    _ok(kernels_lib().xb_expert_gather(dtype_code(x.dtype), out.data_ptr(), x.data_ptr(), perm.data_ptr(), offsets.data_ptr(),
+                                       rows, int(top), offsets.numel() - 1, K, _stream()), "expert_gather")
+
+
 def expert_combine(out, y, inv, top: int):
     T, N = out.shape
     _need(y, "y", torch.float32, (None, N))

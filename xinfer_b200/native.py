@@ -128,5 +128,6 @@ def _declare_kernels(lib):
     _sig(lib, "xb_expert_gemm", I, [I, I, P, P, P, P, P, I, I, I, I, I, I, I, L, L, P])
     _sig(lib, "xb_expert_select_gate", I, [I, P, P, P, P, P, I, P, I, I, I, I, I, P, P])
     _sig(lib, "xb_expert_gemm_mma", I, [I, P, P, P, P, P, I, I, I, I, I, I, I, L, L, P])
+    _sig(lib, "xb_expert_gather", I, [I, P, P, P, P, I, I, I, I, P])
     _sig(lib, "xb_expert_combine", I, [I, P, P, P, I, I, I, P])
     _sig(lib, "xb_attn_decode_tc", I, [P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, F, I, I, I, I, P, I, P, P])

@@ -83,6 +83,7 @@ class StepContext:
     h_q_start: np.ndarray = None
     h_start_pos: np.ndarray = None
     h_slots: np.ndarray = None
+    h_token_ids: np.ndarray = None   # the step's token ids as the host knows them (negative: an id that waits on the device)
     real_tokens: int = 0       # tokens that are not padding
     real_entries: int = 0
     # longest context (start + count) of any entry, and whether every entry brings one token
