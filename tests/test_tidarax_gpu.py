@@ -483,7 +483,7 @@ def test_table_experts_equal_plain(dtype, tensor_cores, dense_up_to, library, E,
 # ---------------------------------------------------------------------------------------------
 # whole models
 # ---------------------------------------------------------------------------------------------
-LENGTHS = {"T1": [70, 45, 130, 33], "T2": [97, 41, 64, 150], "T3": [120, 1, 75, 58]}
+LENGTHS = {"T1": [70, 45, 130, 33], "T2": [97, 41, 64, 150], "T3": [120, 1, 75, 58], "T4": [90, 2, 51, 140]}
 
 
 def _tolerance(dtype, ref, cfg=None, w=None, p=None):
@@ -505,7 +505,7 @@ def _row_error(got, want):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["T1", "T2", "T3"])
+@pytest.mark.parametrize("name", ["T1", "T2", "T3", "T4"])
 def test_every_way_of_cutting_gives_the_plain_logits(name, dtype, tmp_path):
     folder = make_folder(str(tmp_path / "model"), name, torch.float32 if dtype == "float32" else torch.bfloat16)
     ps = prompts(name, LENGTHS[name])

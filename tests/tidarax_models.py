@@ -47,6 +47,13 @@ TINY_T: Dict[str, tuple] = {
         _layer(_left(8, 8, 8, 16, 0.8, dict(dims=2, base=10.0)), 0.6, 100, 1.4, dict(kind="dense", ff=200)),
         _layer(_left(4, 2, 16, 16, 0.6), 1.0, 64, 1.0, _moe(32, 2, 2)),
     ]), 13, 32),
+    # sizes that fit no fast path: a width that is no multiple of 8, an odd recurrence width (the attention's rows
+    # in the shared activation then start at odd offsets), odd feed-forward sizes
+    "T4": (dict(architecture="Tidarax", vocab=61, width=52, norm=dict(eps=2e-6), layers=[
+        _layer(_left(3, 1, 32, 16, 0.5, dict(dims=20, base=3000.0, scaling=dict(factor=5.0, low=1.0, high=3.0, original=40))),
+               1.2, 37, 0.7, _moe(20, 3, 2)),
+        _layer(_left(6, 3, 16, 16, 0.7, dict(dims=16, base=900.0)), 0.8, 44, 1.1, dict(kind="dense", ff=50)),
+    ]), 14, 16),
 }
 
 

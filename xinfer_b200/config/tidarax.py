@@ -147,7 +147,7 @@ class TidaraxConfig:
 
     # ---- the arrangement of parts ---------------------------------------------------------
     def plan(self) -> ModelPlan:
-        def norm(name_unused=None):
+        def norm():
             return NormSpec(kind="rmsnorm", dim=self.width, eps=self.eps, weight_offset=1.0, weight_name="",
                             init="around_zero")
         blocks = []
