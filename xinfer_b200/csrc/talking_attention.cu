@@ -21,13 +21,42 @@
 // q goes to q_out[t, h], k and v into their pages ([page, kv_head, slot, d] and [.., dv]).
 // One block per token, one warp per head at a time; the angles' cos/sin are formed once per token.
 // ------------------------------------------------------------------------------------------
+// Four consecutive elements at once where the row allows it (bfloat16: 8-byte accesses; float32: 16-byte).
+template <typename T>
+__device__ __forceinline__ void load4(const T* p, float (&v)[4]);
+template <>
+__device__ __forceinline__ void load4<float>(const float* p, float (&v)[4]) {
+    const float4 t = *reinterpret_cast<const float4*>(p);
+    v[0] = t.x; v[1] = t.y; v[2] = t.z; v[3] = t.w;
+}
+template <>
+__device__ __forceinline__ void load4<__nv_bfloat16>(const __nv_bfloat16* p, float (&v)[4]) {
+    const uint2 t = *reinterpret_cast<const uint2*>(p);
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&t.y));
+    v[0] = a.x; v[1] = a.y; v[2] = b.x; v[3] = b.y;
+}
+template <typename T>
+__device__ __forceinline__ void store4(T* p, const float (&v)[4]);
+template <>
+__device__ __forceinline__ void store4<float>(float* p, const float (&v)[4]) {
+    *reinterpret_cast<float4*>(p) = make_float4(v[0], v[1], v[2], v[3]);
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* p, const float (&v)[4]) {
+    uint2 t;
+    *reinterpret_cast<__nv_bfloat162*>(&t.x) = __floats2bfloat162_rn(v[0], v[1]);
+    *reinterpret_cast<__nv_bfloat162*>(&t.y) = __floats2bfloat162_rn(v[2], v[3]);
+    *reinterpret_cast<uint2*>(p) = t;
+}
+
 template <typename T>
 __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
                                    const T* __restrict__ qkv, const float* __restrict__ q_w, const float* __restrict__ k_w,
                                    const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                    const int* __restrict__ req_of_token, const int* __restrict__ block_table,
                                    int table_stride, int nh, int nkv, int d, int dv, int rot, int interleaved, int norm_mode,
-                                   int page_size, int num_pages, float eps, int write_kv, int* err) {
+                                   int page_size, int num_pages, float eps, int write_kv, int vec4, int* err) {
     extern __shared__ float sm[];
     const int half = rot / 2;
     float* cs = sm;                 // [half]
@@ -64,7 +93,15 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
             const int g = h - nh - nkv;
             const T* x = row + (size_t)(nh + nkv) * d + (size_t)g * dv;
             T* dst = v_cache + (size_t)(kv_row + (long long)g * page_size) * dv;
-            for (int i = lane; i < dv; i += 32) dst[i] = x[i];
+            if (vec4) {
+                for (int i = lane * 4; i < dv; i += 128) {
+                    float v[4];
+                    load4<T>(x + i, v);
+                    store4<T>(dst + i, v);
+                }
+            } else {
+                for (int i = lane; i < dv; i += 32) dst[i] = x[i];
+            }
             continue;
         }
         const bool is_q = h < nh;
@@ -74,10 +111,22 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
                       : k_cache + (size_t)(kv_row + (long long)(h - nh) * page_size) * d;
         const float* nw = is_q ? q_w : k_w;
         float ss = 0.f;
-        for (int i = lane; i < d; i += 32) {
-            const float v = to_f32<T>(x[i]);
-            xs[i] = v;
-            ss += v * v;
+        if (vec4) {
+            for (int i = lane * 4; i < d; i += 128) {
+                float v[4];
+                load4<T>(x + i, v);
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                    xs[i + k] = v[k];
+                    ss += v[k] * v[k];
+                }
+            }
+        } else {
+            for (int i = lane; i < d; i += 32) {
+                const float v = to_f32<T>(x[i]);
+                xs[i] = v;
+                ss += v * v;
+            }
         }
         __syncwarp();
         if (norm_mode == 1) {
@@ -94,10 +143,20 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
             }
             __syncwarp();
         }
+        float inv = 1.f;
         if (norm_mode == 2) {
             ss = 0.f;
             for (int i = lane; i < d; i += 32) ss += xs[i] * xs[i];
-            const float inv = 1.f / sqrtf(warp_sum(ss) / (float)d + eps);
+            inv = 1.f / sqrtf(warp_sum(ss) / (float)d + eps);
+        }
+        if (vec4) {
+            for (int i = lane * 4; i < d; i += 128) {
+                float v[4];
+#pragma unroll
+                for (int k = 0; k < 4; ++k) v[k] = norm_mode == 2 ? xs[i + k] * inv * (nw ? nw[i + k] : 1.f) : xs[i + k];
+                store4<T>(dst + i, v);
+            }
+        } else if (norm_mode == 2) {
             for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(xs[i] * inv * (nw ? nw[i] : 1.f));
         } else {
             for (int i = lane; i < d; i += 32) dst[i] = from_f32<T>(xs[i]);
@@ -112,18 +171,24 @@ XB_EXPORT int xb_qkv_prepare(int dtype, void* q_out, void* k_cache, void* v_cach
                              int interleaved, int norm_mode, int page_size, int num_pages, float eps, int write_kv, int* err,
                              cudaStream_t stream) {
     if (tokens <= 0) return 0;
-    const int threads = 128;
+    // a warp per head at a time: as many warps as a token has heads, up to 16
+    const int heads = nh + 2 * nkv;
+    const int threads = heads >= 16 ? 512 : (heads >= 8 ? 256 : 128);
     const size_t smem = ((size_t)rot + (size_t)(threads / 32) * d) * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
+    // four elements per access where every head starts on such a boundary, in the rows and in the pages
+    const size_t esz = dtype == XB_F32 ? 4 : 2;
+    const int vec4 = (d % 4 == 0 && dv % 4 == 0 &&
+                      !(((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & (4 * esz - 1))) ? 1 : 0;
     if (dtype == XB_F32)
         qkv_prepare_kernel<float><<<tokens, threads, smem, stream>>>(
             (float*)q_out, (float*)k_cache, (float*)v_cache, (const float*)qkv, q_w, k_w, inv_freq, positions, req_of_token,
-            block_table, table_stride, nh, nkv, d, dv, rot, interleaved, norm_mode, page_size, num_pages, eps, write_kv, err);
+            block_table, table_stride, nh, nkv, d, dv, rot, interleaved, norm_mode, page_size, num_pages, eps, write_kv, vec4, err);
     else
         qkv_prepare_kernel<__nv_bfloat16><<<tokens, threads, smem, stream>>>(
             (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (const __nv_bfloat16*)qkv, q_w, k_w,
             inv_freq, positions, req_of_token, block_table, table_stride, nh, nkv, d, dv, rot, interleaved, norm_mode,
-            page_size, num_pages, eps, write_kv, err);
+            page_size, num_pages, eps, write_kv, vec4, err);
     return xb_launch_status();
 }
 
