@@ -173,8 +173,12 @@ XB_EXPORT int xb_qkv_prepare(int dtype, void* q_out, void* k_cache, void* v_cach
     if (tokens <= 0) return 0;
     // a warp per head at a time: as many warps as a token has heads, up to 16
     const int heads = nh + 2 * nkv;
-    const int threads = heads >= 16 ? 512 : (heads >= 8 ? 256 : 128);
-    const size_t smem = ((size_t)rot + (size_t)(threads / 32) * d) * sizeof(float);
+    int threads = heads >= 16 ? 512 : (heads >= 8 ? 256 : 128);
+    size_t smem = ((size_t)rot + (size_t)(threads / 32) * d) * sizeof(float);
+    while (smem > 48 * 1024 && threads > 32) {     // very wide heads: fewer warps, each still with room for its head
+        threads /= 2;
+        smem = ((size_t)rot + (size_t)(threads / 32) * d) * sizeof(float);
+    }
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     // four elements per access where every head starts on such a boundary, in the rows and in the pages
     const size_t esz = dtype == XB_F32 ? 4 : 2;

@@ -360,7 +360,8 @@ def tidarax_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, h
     layers = 4
     caches = [(bf(num_pages, G, page_size, d), bf(num_pages, G, page_size, d)) for _ in range(layers)]
     q, o = bf(batch, H, d), torch.empty(batch, H * d, dtype=torch.bfloat16, device=device)
-    parts = max(1, min(296 // batch, context // 128, 64))
+    from .parts import talking_attention
+    parts = max(1, min(talking_attention._DECODE_BLOCKS // batch, context // talking_attention._DECODE_MIN_KEYS, 64))
     po = torch.zeros(batch * parts * H * d, dtype=torch.float32, device=device)
     pml = torch.zeros(batch * parts * H * 2, dtype=torch.float32, device=device)
     nbytes = batch * context * G * d * 2 * 2

@@ -24,8 +24,10 @@ from .base import CacheTensor, LayerCache, Mixer, PagedCacheNeed, StepContext, b
 from .linear import linear
 
 _DEFAULT_NAMES = ("q_proj.weight", "k_proj.weight", "v_proj.weight", "o_proj.weight", "talk.weight")
-# a single-token step cuts every token's keys into ranges so that about this many blocks run
-_DECODE_BLOCKS = 296
+# a single-token step cuts every token's keys into ranges so that about this many blocks run: one per SM (the
+# kernel's shared memory allows one block per SM; 8 requests at context 4,096 take 71.7 us in one wave of 144
+# blocks and 80.2 us in 256 blocks)
+_DECODE_BLOCKS = 148
 _DECODE_MIN_KEYS = 128
 # bfloat16: both products on tensor cores where the sizes allow; tests switch it off to compare the two forms
 USE_TENSOR_CORES = True
