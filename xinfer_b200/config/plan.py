@@ -18,7 +18,7 @@ decoder builds from.
 from __future__ import annotations
 
 from dataclasses import dataclass
-from typing import Any, Dict, Optional, Tuple
+from typing import Any, Dict, Optional, Tuple, Union
 
 
 @dataclass(frozen=True)
@@ -47,6 +47,20 @@ class RopeScaling:
 
 
 @dataclass(frozen=True)
+class YarnScaling:
+    """Slower turning for the pairs that turn slowly (the rule of YaRN), decided by how many turns a pair
+    makes within the ``original`` length: with ``pair(t) = rotary_dim * ln(original / (2 pi t)) / (2 ln theta)``
+    the pair index at which ``t`` turns are made, ``lo = max(floor(pair(fast)), 0)``,
+    ``hi = min(ceil(pair(slow)), rotary_dim - 1)`` and ``ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)``,
+    pair i turns at ``f_i / factor * ramp_i + f_i * (1 - ramp_i)``."""
+
+    factor: float
+    original: float
+    fast: float
+    slow: float
+
+
+@dataclass(frozen=True)
 class RopeSpec(PartSpec):
     """Rotary position encoding over the first ``rotary_dim`` channels of each head.
 
@@ -54,6 +68,7 @@ class RopeSpec(PartSpec):
     ``scaling`` changes the frequencies (None: ``theta^(-2j / rotary_dim)`` as they are).
     ``tables`` False: no cos/sin table is built; kernels take the frequencies and form
     ``position * frequency`` in float32 themselves, so no longest position has to be known.
+    ``magnitude``: cos and sin are both multiplied by it (1: a pure rotation).
     """
 
     head_dim: int = 0
@@ -61,8 +76,9 @@ class RopeSpec(PartSpec):
     theta: float = 10000.0
     max_positions: int = 0
     layout: str = "neox"
-    scaling: Optional[RopeScaling] = None
+    scaling: Optional[Union[RopeScaling, YarnScaling]] = None
     tables: bool = True
+    magnitude: float = 1.0
 
 
 @dataclass(frozen=True)
@@ -75,6 +91,17 @@ class NormSpec(PartSpec):
     weight_name: str = "weight"
     # how the random-weights mode draws the weight: "norm" (around one) or "around_zero"
     init: str = "norm"
+
+
+@dataclass(frozen=True)
+class DynamicTanhSpec(PartSpec):
+    """A norm without statistics: ``y = tanh(alpha * x) * w + b`` with a learned scalar ``alpha`` and learned
+    vectors ``w`` and ``b``.  The three names follow the part's prefix."""
+
+    dim: int = 0
+    weight_name: str = "weight"
+    bias_name: str = "bias"
+    alpha_name: str = "alpha"
 
 
 @dataclass(frozen=True)
@@ -109,6 +136,36 @@ class AttentionSpec(PartSpec):
 
 
 @dataclass(frozen=True)
+class LatentAttentionSpec(PartSpec):
+    """Attention whose keys and values are linear maps of one cached latent vector per token.
+
+    A token's ``kv_rank`` latent channels (RMS-normed with a learned weight, ``norm_eps``) and one rotated key part
+    of ``rope_dim`` channels shared by all heads are all that is cached.  Head h has ``head_dim`` plain and
+    ``rope_dim`` rotated query channels; its plain key is ``W_uk,h c`` and its value ``W_uv,h c`` (``v_head_dim``
+    channels).  ``window`` as for attention.  ``sink``: every head's softmax has one more entry with a learned score
+    and no value.  ``gate``: the concatenated heads are multiplied by ``sigmoid(W_g h)`` before the output projection.
+    ``shares_cache``: the layer has no latent projection of its own and reads the rows another layer cached.
+    ``cache_window``: how long cached rows must be kept (None: for ever): the largest window among the layers that
+    read them.  ``names``: the tensors q, latent projection, its norm, uk, uv, sink, gate, output after the prefix."""
+
+    hidden: int = 0
+    num_heads: int = 0
+    head_dim: int = 0
+    rope_dim: int = 0
+    v_head_dim: int = 0
+    kv_rank: int = 0
+    scale: float = 1.0
+    rope: Optional[RopeSpec] = None
+    window: Optional[int] = None
+    cache_window: Optional[int] = None
+    norm_eps: float = 1e-6
+    sink: bool = False
+    gate: bool = False
+    shares_cache: bool = False
+    names: Tuple[str, ...] = ("q", "dkv", "dkv.norm", "uk", "uv", "sink", "g", "o")
+
+
+@dataclass(frozen=True)
 class GatedRecurrenceSpec(PartSpec):
     """A recurrence over ``width`` channels whose gates read only the current token (minGRU):
     z = sigmoid(W_z h + b_z), u = W_x h + b_x, candidate c = u + 1/2 where u >= 0 and sigmoid(u)
@@ -136,6 +193,8 @@ class FeedForwardSpec(PartSpec):
     intermediate: int = 0
     activation: str = "silu"
     eps: float = 1e-6      # of activations that norm (polynorm)
+    # tensor names of the gate, up and down matrices after the part's prefix; None: the "gate_proj.weight" family
+    names: Optional[Tuple[str, ...]] = None
 
 
 @dataclass(frozen=True)
@@ -158,19 +217,21 @@ class BlockOp:
 
     * ``op="norm"``: ``dst = norm(src)`` with the norm ``spec``;
     * ``op="mixer"`` / ``op="feed_forward"``: ``dst = part(src)`` with the part ``spec``;
-    * ``op="add"``: ``dst = dst + src`` (no spec).
+    * ``op="add"``: ``dst = dst + scale * src`` (no spec).
 
     ``name`` is the tensor-name piece between the block's prefix and the part's own tensor names;
     two operations with the same ``op`` and ``name`` are the same part (one set of weights).
     An addition into a value is carried out when that value is next read: by the norm kernel
     that reads it where a norm follows (sum and norm in one pass, the sum in float32), by an
-    addition kernel otherwise."""
+    addition kernel otherwise.  A norm of a block-local value that is only added into another value afterwards
+    may likewise be carried out by the kernel that forms that sum, where its kind offers that."""
 
     op: str
     src: str
     dst: str
     spec: Optional[PartSpec] = None
     name: str = ""
+    scale: float = 1.0
 
 
 BLOCK_OPS = ("norm", "mixer", "feed_forward", "add")
@@ -199,7 +260,7 @@ class BlockSpec:
         ops = self.ops_of("feed_forward")
         return ops[0].spec if ops else None
 
-    def norms(self) -> Tuple[NormSpec, ...]:
+    def norms(self) -> Tuple[PartSpec, ...]:
         return tuple(o.spec for o in self.ops_of("norm"))
 
     def validate(self) -> None:
@@ -218,6 +279,8 @@ class BlockSpec:
                     raise ValueError(f"{where}: an addition has no part")
                 if o.src == o.dst:
                     raise ValueError(f"{where}: adds '{o.src}' to itself")
+            elif o.scale != 1.0:
+                raise ValueError(f"{where}: only an addition has a scale")
             else:
                 if o.spec is None:
                     raise ValueError(f"{where}: needs a part spec")
@@ -263,7 +326,7 @@ class ModelPlan:
     embed_name: str
     blocks: Tuple[BlockSpec, ...]
     runs: Tuple[LayerRun, ...]
-    final_norm: NormSpec
+    final_norm: PartSpec
     final_norm_name: str  # tensor-name prefix of the final norm
     # None = the head reuses the embedding table
     head_name: Optional[str]

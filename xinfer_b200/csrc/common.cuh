@@ -67,6 +67,22 @@ __device__ __forceinline__ float block_sum(float v, float* scratch /* >= 33 floa
 // the float32 path divides and exponentiates exactly.
 __device__ __forceinline__ float silu_mul_bf16(float g, float u) { return __fdividef(g, 1.f + __expf(-g)) * u; }
 
+// Activations of a gated feed-forward, act(g) * u, by code (shared with the Python side).
+#define XB_ACT_SILU 0
+#define XB_ACT_GELU_TANH 1
+// gelu in its tanh form: 0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3))), float32 throughout
+__device__ __forceinline__ float gelu_tanh_f32(float z) {
+    return 0.5f * z * (1.f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+template <int ACT>
+__device__ __forceinline__ float gate_mul_bf16(float g, float u) {
+    return ACT == XB_ACT_GELU_TANH ? gelu_tanh_f32(g) * u : silu_mul_bf16(g, u);
+}
+template <int ACT>
+__device__ __forceinline__ float gate_mul_f32(float g, float u) {
+    return ACT == XB_ACT_GELU_TANH ? gelu_tanh_f32(g) * u : g / (1.f + expf(-g)) * u;
+}
+
 // Last CUDA error of a launch as an int for the caller (0 = ok).
 static inline int xb_launch_status() { return (int)cudaGetLastError(); }
 

@@ -99,7 +99,7 @@ __global__ void __launch_bounds__(1024) rmsnorm_bf16_kernel(__nv_bfloat16* __res
 // grid (blocks along a row, rows); a thread takes SWIGLU_UNROLL vectors of the row, all loads first
 // (one vector when there is too little work to fill the device that way).
 constexpr int SWIGLU_THREADS = 128;
-template <int SWIGLU_UNROLL>
+template <int SWIGLU_UNROLL, int ACT>
 __global__ void __launch_bounds__(SWIGLU_THREADS)
 swiglu_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int inter, int tokens) {
     pdl_launch_dependents();
@@ -125,7 +125,7 @@ swiglu_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
                 unpack8(pg[k], g);
                 unpack8(pu[k], u);
 #pragma unroll
-                for (int e = 0; e < 8; ++e) y[e] = silu_mul_bf16(g[e], u[e]);
+                for (int e = 0; e < 8; ++e) y[e] = gate_mul_bf16<ACT>(g[e], u[e]);
                 reinterpret_cast<Pack8*>(out + (size_t)t * inter)[c] = pack8(y);
             }
         }
@@ -136,6 +136,7 @@ swiglu_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restr
 // grid (blocks along a row, row walkers): a block takes U vectors per thread of rows blockIdx.y,
 // blockIdx.y + gridDim.y, ...; the next row's vectors are requested before this row's are computed.
 constexpr int SG_THREADS = 128, SG_U = 4;
+template <int ACT>
 __global__ void __launch_bounds__(SG_THREADS)
 swiglu_rows_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __restrict__ gu, int inter, int tokens) {
     pdl_launch_dependents();
@@ -164,7 +165,7 @@ swiglu_rows_bf16_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* __
             unpack8(pg[k], g);
             unpack8(pu[k], u);
 #pragma unroll
-            for (int e = 0; e < 8; ++e) y[k][e] = silu_mul_bf16(g[e], u[e]);
+            for (int e = 0; e < 8; ++e) y[k][e] = gate_mul_bf16<ACT>(g[e], u[e]);
         }
         const int next = t + gridDim.y;
         if (next < tokens) fetch(next);
@@ -228,23 +229,30 @@ XB_EXPORT int xb_rmsnorm_bf16(void* out, void* sum_out, const void* x, const voi
     return (int)cudaErrorInvalidValue;
 }
 
-XB_EXPORT int xb_swiglu_bf16(void* out, const void* gu, int tokens, int inter, cudaStream_t stream) {
-    if (tokens <= 0 || inter <= 0) return 0;
-    if (inter % 8) return (int)cudaErrorInvalidValue;
+// act: XB_ACT_SILU or XB_ACT_GELU_TANH (the gate's activation)
+template <int ACT>
+static int swiglu_bf16_launch(void* out, const void* gu, int tokens, int inter, cudaStream_t stream) {
     const int vpr = inter / 8;
     const unsigned rows = (unsigned)(tokens < 65535 ? tokens : 65535);
     if ((long long)tokens * vpr >= 148LL * 2048 * 2) {
         const int per_block = SWIGLU_THREADS * 4;
-        return xb_launch(swiglu_bf16_kernel<4>, dim3((unsigned)((vpr + per_block - 1) / per_block), rows), dim3(SWIGLU_THREADS), 0,
+        return xb_launch(swiglu_bf16_kernel<4, ACT>, dim3((unsigned)((vpr + per_block - 1) / per_block), rows), dim3(SWIGLU_THREADS), 0,
                          stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, inter, tokens);
     }
-    return xb_launch(swiglu_bf16_kernel<1>, dim3((unsigned)((vpr + SWIGLU_THREADS - 1) / SWIGLU_THREADS), rows), dim3(SWIGLU_THREADS), 0,
+    return xb_launch(swiglu_bf16_kernel<1, ACT>, dim3((unsigned)((vpr + SWIGLU_THREADS - 1) / SWIGLU_THREADS), rows), dim3(SWIGLU_THREADS), 0,
                      stream, (__nv_bfloat16*)out, (const __nv_bfloat16*)gu, inter, tokens);
+}
+
+XB_EXPORT int xb_swiglu_bf16(void* out, const void* gu, int tokens, int inter, int act, cudaStream_t stream) {
+    if (tokens <= 0 || inter <= 0) return 0;
+    if (inter % 8) return (int)cudaErrorInvalidValue;
+    return act == XB_ACT_GELU_TANH ? swiglu_bf16_launch<XB_ACT_GELU_TANH>(out, gu, tokens, inter, stream)
+                                   : swiglu_bf16_launch<XB_ACT_SILU>(out, gu, tokens, inter, stream);
 }
 
 // The SiLU gate for many rows (a prompt portion): about eight blocks per SM stay resident and walk over
 // the rows with the next row requested early; the same values as xb_swiglu_bf16.
-XB_EXPORT int xb_swiglu_rows_bf16(void* out, const void* gu, int tokens, int inter, cudaStream_t stream) {
+XB_EXPORT int xb_swiglu_rows_bf16(void* out, const void* gu, int tokens, int inter, int act, cudaStream_t stream) {
     if (tokens <= 0 || inter <= 0) return 0;
     if (inter % 8) return (int)cudaErrorNotSupported;
     const int vpr = inter / 8;
@@ -253,7 +261,10 @@ XB_EXPORT int xb_swiglu_rows_bf16(void* out, const void* gu, int tokens, int int
     // about eight blocks per SM stay resident and walk over the rows
     unsigned by = (148u * 8u + bx - 1) / bx;
     if (by > (unsigned)tokens) by = (unsigned)tokens;
-    return xb_launch(swiglu_rows_bf16_kernel, dim3(bx, by), dim3(SG_THREADS), 0, stream, (__nv_bfloat16*)out,
+    if (act == XB_ACT_GELU_TANH)
+        return xb_launch(swiglu_rows_bf16_kernel<XB_ACT_GELU_TANH>, dim3(bx, by), dim3(SG_THREADS), 0, stream, (__nv_bfloat16*)out,
+                         (const __nv_bfloat16*)gu, inter, tokens);
+    return xb_launch(swiglu_rows_bf16_kernel<XB_ACT_SILU>, dim3(bx, by), dim3(SG_THREADS), 0, stream, (__nv_bfloat16*)out,
                      (const __nv_bfloat16*)gu, inter, tokens);
 }
 

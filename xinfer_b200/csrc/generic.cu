@@ -126,22 +126,22 @@ XB_EXPORT int xb_rmsnorm(int dtype, void* out, void* sum_out, const void* x, con
 }
 
 // ------------------------------------------------------------------------------------------
-// out[t] = x[t] + branch[t]  (float32 sum, rounded to T); used where no norm follows.
+// out[t] = x[t] + scale * branch[t]  (float32 sum, rounded to T); used where no norm follows.
 // ------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void add_kernel(T* out, const T* x, const T* branch, size_t n) {
+__global__ void add_kernel(T* out, const T* x, const T* branch, size_t n, float scale) {
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = from_f32<T>(to_f32<T>(x[i]) + to_f32<T>(branch[i]));
+    if (i < n) out[i] = from_f32<T>(scale == 1.f ? to_f32<T>(x[i]) + to_f32<T>(branch[i]) : fmaf(scale, to_f32<T>(branch[i]), to_f32<T>(x[i])));
 }
 
-XB_EXPORT int xb_add(int dtype, void* out, const void* x, const void* branch, long long n, cudaStream_t stream) {
+XB_EXPORT int xb_add(int dtype, void* out, const void* x, const void* branch, long long n, float scale, cudaStream_t stream) {
     if (n <= 0) return 0;
     const int threads = 256;
     const unsigned blocks = (unsigned)((n + threads - 1) / threads);
     if (dtype == XB_F32)
-        add_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, (const float*)x, (const float*)branch, (size_t)n);
+        add_kernel<float><<<blocks, threads, 0, stream>>>((float*)out, (const float*)x, (const float*)branch, (size_t)n, scale);
     else
-        add_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)x, (const __nv_bfloat16*)branch, (size_t)n);
+        add_kernel<__nv_bfloat16><<<blocks, threads, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)x, (const __nv_bfloat16*)branch, (size_t)n, scale);
     return xb_launch_status();
 }
 
@@ -363,13 +363,18 @@ XB_EXPORT int xb_qk_norm_rope_write(
 // position order with a running maximum, so a query's result depends only on its own position
 // and the keys before it.  Scores, softmax and the value sum are float32.
 //   keys seen by a query at position p:  max(0, p - window + 1) .. p   (window <= 0: from 0)
+// Keys have d channels and values dv; the row of (page, kv head, slot) starts k_stride (v_stride)
+// elements after the row before it, so keys and values may be columns of one cached row (a latent
+// vector whose first dv channels are the value).  A query row starts at q + t * q_ts + h * q_hs.
+// `sink` (per head, nullable): one more softmax entry of that score that carries no value.
 // ------------------------------------------------------------------------------------------
 template <typename T, int MAXE>
 __global__ void attention_plain_kernel(
-    T* __restrict__ out, const T* __restrict__ q, const T* __restrict__ k_cache,
-    const T* __restrict__ v_cache, const int* __restrict__ positions,
+    T* __restrict__ out, const T* __restrict__ q, long long q_ts, long long q_hs, const T* __restrict__ k_cache,
+    const T* __restrict__ v_cache, int k_stride, int v_stride, const float* __restrict__ sink,
+    const int* __restrict__ positions,
     const int* __restrict__ req_of_token, const int* __restrict__ block_table, int table_stride,
-    int nh, int nkv, int d, int page_size, int num_pages, int window, float scale, int* err) {
+    int nh, int nkv, int d, int dv, int page_size, int num_pages, int window, float scale, int* err) {
     const int t = blockIdx.x;
     const int lane = threadIdx.x & 31;
     const int h = blockIdx.y * (blockDim.x >> 5) + (threadIdx.x >> 5);
@@ -378,12 +383,12 @@ __global__ void attention_plain_kernel(
     const int pos = positions[t];
     const int b = req_of_token[t];
     if (b < 0) {  // padding token
-        T* o = out + ((size_t)t * nh + h) * d;
-        for (int i = lane; i < d; i += 32) o[i] = from_f32<T>(0.f);
+        T* o = out + ((size_t)t * nh + h) * dv;
+        for (int i = lane; i < dv; i += 32) o[i] = from_f32<T>(0.f);
         return;
     }
     const int* table = block_table + (size_t)b * table_stride;
-    const T* qv = q + ((size_t)t * nh + h) * d;
+    const T* qv = q + (size_t)t * q_ts + (size_t)h * q_hs;
     float qr[MAXE], acc[MAXE];
 #pragma unroll
     for (int e = 0; e < MAXE; ++e) {
@@ -392,6 +397,10 @@ __global__ void attention_plain_kernel(
         acc[e] = 0.f;
     }
     float m = -INFINITY, l = 0.f;
+    if (sink) {   // the entry without a key: exp(sink - m) with m = sink
+        m = sink[h];
+        l = 1.f;
+    }
     const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
     for (int j = lo; j <= pos; ++j) {
         const int page = table[j / page_size];
@@ -400,8 +409,8 @@ __global__ void attention_plain_kernel(
             continue;
         }
         const size_t rowi = ((size_t)page * nkv + g) * page_size + (j % page_size);
-        const T* kr = k_cache + rowi * d;
-        const T* vr = v_cache + rowi * d;
+        const T* kr = k_cache + rowi * k_stride;
+        const T* vr = v_cache + rowi * v_stride;
         float s = 0.f;
 #pragma unroll
         for (int e = 0; e < MAXE; ++e) {
@@ -416,72 +425,85 @@ __global__ void attention_plain_kernel(
 #pragma unroll
         for (int e = 0; e < MAXE; ++e) {
             const int i = e * 32 + lane;
-            if (i < d) acc[e] = acc[e] * corr + p * to_f32<T>(vr[i]);
+            if (i < dv) acc[e] = acc[e] * corr + p * to_f32<T>(vr[i]);
         }
         m = m_new;
     }
     const float inv = l > 0.f ? 1.f / l : 0.f;
-    T* o = out + ((size_t)t * nh + h) * d;
+    T* o = out + ((size_t)t * nh + h) * dv;
 #pragma unroll
     for (int e = 0; e < MAXE; ++e) {
         const int i = e * 32 + lane;
-        if (i < d) o[i] = from_f32<T>(acc[e] * inv);
+        if (i < dv) o[i] = from_f32<T>(acc[e] * inv);
     }
 }
 
 template <typename T>
-static int attention_plain_launch(void* out, const void* q, const void* kc, const void* vc,
+static int attention_plain_launch(void* out, const void* q, long long q_ts, long long q_hs, const void* kc, const void* vc,
+                                  int k_stride, int v_stride, const float* sink,
                                   const int* positions, const int* req_of_token, const int* block_table,
-                                  int table_stride, int tokens, int nh, int nkv, int d, int page_size,
+                                  int table_stride, int tokens, int nh, int nkv, int d, int dv, int page_size,
                                   int num_pages, int window, float scale, int* err, cudaStream_t stream) {
     dim3 grid(tokens, (nh + 3) / 4);
+    const int dm = d > dv ? d : dv;
 #define XB_ATT(MAXE)                                                                              \
     attention_plain_kernel<T, MAXE><<<grid, 128, 0, stream>>>(                                    \
-        (T*)out, (const T*)q, (const T*)kc, (const T*)vc, positions, req_of_token, block_table,   \
-        table_stride, nh, nkv, d, page_size, num_pages, window, scale, err)
-    if (d <= 64) XB_ATT(2);
-    else if (d <= 128) XB_ATT(4);
-    else if (d <= 256) XB_ATT(8);
-    else if (d <= 512) XB_ATT(16);
+        (T*)out, (const T*)q, q_ts, q_hs, (const T*)kc, (const T*)vc, k_stride, v_stride, sink,  \
+        positions, req_of_token, block_table,                                                    \
+        table_stride, nh, nkv, d, dv, page_size, num_pages, window, scale, err)
+    if (dm <= 64) XB_ATT(2);
+    else if (dm <= 128) XB_ATT(4);
+    else if (dm <= 256) XB_ATT(8);
+    else if (dm <= 512) XB_ATT(16);
+    else if (dm <= 768) XB_ATT(24);
+    else if (dm <= 1024) XB_ATT(32);
     else return (int)cudaErrorInvalidValue;
 #undef XB_ATT
     return xb_launch_status();
 }
 
-XB_EXPORT int xb_attention_plain(int dtype, void* out, const void* q, const void* k_cache,
-                                 const void* v_cache, const int* positions, const int* req_of_token,
+XB_EXPORT int xb_attention_plain(int dtype, void* out, const void* q, long long q_ts, long long q_hs, const void* k_cache,
+                                 const void* v_cache, int k_stride, int v_stride, const float* sink,
+                                 const int* positions, const int* req_of_token,
                                  const int* block_table, int table_stride, int tokens, int nh, int nkv,
-                                 int d, int page_size, int num_pages, int window, float scale, int* err,
+                                 int d, int dv, int page_size, int num_pages, int window, float scale, int* err,
                                  cudaStream_t stream) {
     if (tokens <= 0) return 0;
     if (dtype == XB_F32)
-        return attention_plain_launch<float>(out, q, k_cache, v_cache, positions, req_of_token, block_table,
-                                             table_stride, tokens, nh, nkv, d, page_size, num_pages, window, scale, err, stream);
-    return attention_plain_launch<__nv_bfloat16>(out, q, k_cache, v_cache, positions, req_of_token, block_table,
-                                                 table_stride, tokens, nh, nkv, d, page_size, num_pages, window, scale, err, stream);
+        return attention_plain_launch<float>(out, q, q_ts, q_hs, k_cache, v_cache, k_stride, v_stride, sink, positions,
+                                             req_of_token, block_table,
+                                             table_stride, tokens, nh, nkv, d, dv, page_size, num_pages, window, scale, err, stream);
+    return attention_plain_launch<__nv_bfloat16>(out, q, q_ts, q_hs, k_cache, v_cache, k_stride, v_stride, sink, positions,
+                                                 req_of_token, block_table,
+                                                 table_stride, tokens, nh, nkv, d, dv, page_size, num_pages, window, scale, err, stream);
 }
 
 // ------------------------------------------------------------------------------------------
-// Gated activation: out[t, i] = silu(gu[t, i]) * gu[t, I + i], silu(z) = z / (1 + exp(-z)).
+// Gated activation: out[t, i] = act(gu[t, i]) * gu[t, I + i]; act = silu, z / (1 + exp(-z)), or
+// gelu in its tanh form.
 // ------------------------------------------------------------------------------------------
-template <typename T>
+template <typename T, int ACT>
 __global__ void swiglu_kernel(T* __restrict__ out, const T* __restrict__ gu, int inter, size_t n) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
     const size_t t = i / inter, c = i % inter;
     const float g = to_f32<T>(gu[t * 2 * inter + c]);
     const float u = to_f32<T>(gu[t * 2 * inter + inter + c]);
-    out[i] = from_f32<T>(sizeof(T) == 2 ? silu_mul_bf16(g, u) : g / (1.f + expf(-g)) * u);
+    out[i] = from_f32<T>(sizeof(T) == 2 ? gate_mul_bf16<ACT>(g, u) : gate_mul_f32<ACT>(g, u));
 }
 
-XB_EXPORT int xb_swiglu(int dtype, void* out, const void* gu, int tokens, int inter, cudaStream_t stream) {
+XB_EXPORT int xb_swiglu(int dtype, void* out, const void* gu, int tokens, int inter, int act, cudaStream_t stream) {
     const size_t n = (size_t)tokens * inter;
     if (n == 0) return 0;
     const unsigned blocks = (unsigned)((n + 255) / 256);
-    if (dtype == XB_F32)
-        swiglu_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, (const float*)gu, inter, n);
-    else
-        swiglu_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)gu, inter, n);
+    typedef __nv_bfloat16 bf;
+    if (dtype == XB_F32) {
+        if (act == XB_ACT_GELU_TANH) swiglu_kernel<float, XB_ACT_GELU_TANH><<<blocks, 256, 0, stream>>>((float*)out, (const float*)gu, inter, n);
+        else swiglu_kernel<float, XB_ACT_SILU><<<blocks, 256, 0, stream>>>((float*)out, (const float*)gu, inter, n);
+    } else {
+        if (act == XB_ACT_GELU_TANH) swiglu_kernel<bf, XB_ACT_GELU_TANH><<<blocks, 256, 0, stream>>>((bf*)out, (const bf*)gu, inter, n);
+        else swiglu_kernel<bf, XB_ACT_SILU><<<blocks, 256, 0, stream>>>((bf*)out, (const bf*)gu, inter, n);
+    }
     return xb_launch_status();
 }
 

@@ -92,17 +92,17 @@ XB_EXPORT int xb_rmsnorm_f32(int branch_dtype, int out_dtype, void* out, float* 
 }
 
 template <typename TB>
-__global__ void add_f32_kernel(float* out, const float* x, const TB* branch, size_t n) {
+__global__ void add_f32_kernel(float* out, const float* x, const TB* branch, size_t n, float scale) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i < n) out[i] = x[i] + to_f32<TB>(branch[i]);
+    if (i < n) out[i] = scale == 1.f ? x[i] + to_f32<TB>(branch[i]) : fmaf(scale, to_f32<TB>(branch[i]), x[i]);
 }
 
-XB_EXPORT int xb_add_f32(int branch_dtype, float* out, const float* x, const void* branch, long long n, cudaStream_t stream) {
+XB_EXPORT int xb_add_f32(int branch_dtype, float* out, const float* x, const void* branch, long long n, float scale, cudaStream_t stream) {
     if (n <= 0) return 0;
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (branch_dtype == XB_F32)
-        add_f32_kernel<float><<<blocks, 256, 0, stream>>>(out, x, (const float*)branch, (size_t)n);
+        add_f32_kernel<float><<<blocks, 256, 0, stream>>>(out, x, (const float*)branch, (size_t)n, scale);
     else
-        add_f32_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(out, x, (const __nv_bfloat16*)branch, (size_t)n);
+        add_f32_kernel<__nv_bfloat16><<<blocks, 256, 0, stream>>>(out, x, (const __nv_bfloat16*)branch, (size_t)n, scale);
     return xb_launch_status();
 }

@@ -16,7 +16,8 @@
 // ------------------------------------------------------------------------------------------
 // qkv[t] = [heads x d | kv_heads x d | kv_heads x dv].  Per q/k head, in this order:
 //   norm_mode 1: x <- x / rms(x) * w      (w absent: 1)
-//   rotation of the first `rot` channels by position * inv_freq[pair]  (inv_freq absent: none)
+//   rotation of the first `rot` channels by position * inv_freq[pair]  (inv_freq absent: none);
+//     cos and sin are multiplied by rot_mag (1: a pure rotation)
 //   norm_mode 2: x <- x / rms(x) * w
 // q goes to q_out[t, h], k and v into their pages ([page, kv_head, slot, d] and [.., dv]).
 // One block per token, one warp per head at a time; the angles' cos/sin are formed once per token.
@@ -56,7 +57,7 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
                                    const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                    const int* __restrict__ req_of_token, const int* __restrict__ block_table,
                                    int table_stride, int nh, int nkv, int d, int dv, int rot, int interleaved, int norm_mode,
-                                   int page_size, int num_pages, float eps, int write_kv, int vec4, int* err) {
+                                   int page_size, int num_pages, float eps, int write_kv, int vec4, float rot_mag, int* err) {
     extern __shared__ float sm[];
     const int half = rot / 2;
     float* cs = sm;                 // [half]
@@ -71,8 +72,8 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
             const float a = (float)pos * inv_freq[j];
             float s, c;
             sincosf(a, &s, &c);
-            cs[j] = c;
-            sn[j] = s;
+            cs[j] = c * rot_mag;
+            sn[j] = s * rot_mag;
         }
     }
     __syncthreads();
@@ -168,7 +169,7 @@ __global__ void qkv_prepare_kernel(T* __restrict__ q_out, T* __restrict__ k_cach
 XB_EXPORT int xb_qkv_prepare(int dtype, void* q_out, void* k_cache, void* v_cache, const void* qkv, const float* q_w,
                              const float* k_w, const float* inv_freq, const int* positions, const int* req_of_token,
                              const int* block_table, int table_stride, int tokens, int nh, int nkv, int d, int dv, int rot,
-                             int interleaved, int norm_mode, int page_size, int num_pages, float eps, int write_kv, int* err,
+                             int interleaved, int norm_mode, int page_size, int num_pages, float eps, int write_kv, float rot_mag, int* err,
                              cudaStream_t stream) {
     if (tokens <= 0) return 0;
     // a warp per head at a time: as many warps as a token has heads, up to 16
@@ -187,12 +188,12 @@ XB_EXPORT int xb_qkv_prepare(int dtype, void* q_out, void* k_cache, void* v_cach
     if (dtype == XB_F32)
         qkv_prepare_kernel<float><<<tokens, threads, smem, stream>>>(
             (float*)q_out, (float*)k_cache, (float*)v_cache, (const float*)qkv, q_w, k_w, inv_freq, positions, req_of_token,
-            block_table, table_stride, nh, nkv, d, dv, rot, interleaved, norm_mode, page_size, num_pages, eps, write_kv, vec4, err);
+            block_table, table_stride, nh, nkv, d, dv, rot, interleaved, norm_mode, page_size, num_pages, eps, write_kv, vec4, rot_mag, err);
     else
         qkv_prepare_kernel<__nv_bfloat16><<<tokens, threads, smem, stream>>>(
             (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_cache, (__nv_bfloat16*)v_cache, (const __nv_bfloat16*)qkv, q_w, k_w,
             inv_freq, positions, req_of_token, block_table, table_stride, nh, nkv, d, dv, rot, interleaved, norm_mode,
-            page_size, num_pages, eps, write_kv, vec4, err);
+            page_size, num_pages, eps, write_kv, vec4, rot_mag, err);
     return xb_launch_status();
 }
 

@@ -205,17 +205,56 @@ def rmsnorm(out, x, weight, eps, err, *, branch=None, sum_out=None, rows=None, w
                                  float(weight_offset), err.data_ptr(), _stream()), "rmsnorm")
 
 
-def add(out, x, branch):
+def add(out, x, branch, scale: float = 1.0):
+    """out = x + scale * branch (the sum in float32)."""
     _need(x, "x")
     if x.dtype == torch.float32 and branch.dtype != torch.float32:
         _need(branch, "branch", None, tuple(x.shape))
         _need(out, "out", torch.float32, tuple(x.shape))
         _ok(kernels_lib().xb_add_f32(dtype_code(branch.dtype), out.data_ptr(), x.data_ptr(), branch.data_ptr(), x.numel(),
-                                     _stream()), "add_f32")
+                                     float(scale), _stream()), "add_f32")
         return
     _need(branch, "branch", x.dtype, tuple(x.shape))
     _need(out, "out", x.dtype, tuple(x.shape))
-    _ok(kernels_lib().xb_add(dtype_code(x.dtype), out.data_ptr(), x.data_ptr(), branch.data_ptr(), x.numel(), _stream()), "add")
+    _ok(kernels_lib().xb_add(dtype_code(x.dtype), out.data_ptr(), x.data_ptr(), branch.data_ptr(), x.numel(), float(scale),
+                             _stream()), "add")
+
+
+def dyt_norm(out, x, alpha, weight, bias, err, *, branch=None, branch_scale: float = 1.0, branch_norm=None, sum_out=None,
+             rows=None):
+    """Dynamic Tanh: out = tanh(alpha * s) * weight + bias with s = x + branch_scale * br, optionally gathered at
+    ``rows``; ``br`` is the branch, or with ``branch_norm`` = (alpha, weight, bias) its own Dynamic Tanh first.
+    ``sum_out`` receives s (it may be x itself when no rows are given); ``out`` None: only the sum is formed.
+    x and sum_out share a type, the branch and out may have another; the arithmetic is float32."""
+    dim = x.shape[-1]
+    n = out.shape[0] if out is not None else x.shape[0]
+    _need(x, "x", None, (None, dim))
+    for name, t, shape in (("alpha", alpha, ()), ("weight", weight, (dim,)), ("bias", bias, (dim,))):
+        _need(t, name, torch.float32, shape)
+    if out is not None:
+        _need(out, "out", None, (n, dim))
+    if branch is not None:
+        _need(branch, "branch", None, tuple(x.shape))
+    if branch_norm is not None:
+        if branch is None:
+            raise KernelError("a branch norm needs a branch")
+        for name, t, shape in (("branch alpha", branch_norm[0], ()), ("branch weight", branch_norm[1], (dim,)),
+                               ("branch bias", branch_norm[2], (dim,))):
+            _need(t, name, torch.float32, shape)
+    if sum_out is not None:
+        _need(sum_out, "sum_out", x.dtype, (n, dim))
+    if rows is not None:
+        _need(rows, "rows", torch.int32)
+        if rows.numel() < n:
+            raise KernelError(f"rows holds {rows.numel()} entries for {n} output rows")
+    elif n != x.shape[0]:
+        raise KernelError(f"out has {n} rows, x has {x.shape[0]} and no row list was given")
+    bn = branch_norm or (None, None, None)
+    _ok(kernels_lib().xb_dyt_norm(dtype_code(x.dtype), dtype_code(branch.dtype) if branch is not None else F32,
+                                  dtype_code(out.dtype) if out is not None else F32, _ptr(out), _ptr(sum_out), x.data_ptr(),
+                                  _ptr(branch), _ptr(rows), alpha.data_ptr(), weight.data_ptr(), bias.data_ptr(),
+                                  float(branch_scale), _ptr(bn[0]), _ptr(bn[1]), _ptr(bn[2]), n, dim, x.shape[0],
+                                  err.data_ptr(), _stream()), "dyt_norm")
 
 
 def gemm_plain(out, a, w):
@@ -270,34 +309,55 @@ def qk_norm_rope_write(q_out, k_cache, v_cache, qkv, q_w, k_w, cos_t, sin_t, pos
         int(bool(write_kv)), err.data_ptr(), _stream()), "qk_norm_rope_write")
 
 
-def attention_plain(out, q, k_cache, v_cache, positions, req_of_token, block_table, table_stride, window, scale, err):
+def attention_plain(out, q, k_cache, v_cache, positions, req_of_token, block_table, table_stride, window, scale, err, *,
+                    sink=None, value_dim=None):
+    """Attention of every token over its request's cached positions, one warp per (token, head), float32 scores,
+    softmax and value sums.  ``q`` is ``[T, heads, d]``, ``out`` ``[T, heads, dv]``.  The caches are
+    ``[page, kv_head, slot, d]`` and ``[page, kv_head, slot, dv]``; with ``value_dim`` the values are the first
+    ``value_dim`` channels of the key rows themselves (``v_cache`` is then ignored).  ``sink`` (float32 per head):
+    one more softmax entry of that score without a value."""
     T, nh, d = q.shape
     _need(q, "q", None, (T, nh, d))
-    _need(out, "out", q.dtype, (T, nh, d))
     _need(k_cache, "k_cache", q.dtype, (None, None, None, d))
-    _need(v_cache, "v_cache", q.dtype, tuple(k_cache.shape))
     num_pages, nkv, page_size, _ = k_cache.shape
+    if value_dim is not None:
+        dv = int(value_dim)
+        if not (0 < dv <= d):
+            raise KernelError(f"values of {dv} channels cannot be the first channels of {d}-channel keys")
+        v_cache, v_stride = k_cache, d
+    else:
+        dv = v_cache.shape[-1]
+        _need(v_cache, "v_cache", q.dtype, (num_pages, nkv, page_size, dv))
+        v_stride = dv
+    _need(out, "out", q.dtype, (T, nh, dv))
+    if sink is not None:
+        _need(sink, "sink", torch.float32, (nh,))
     if nh % nkv:
         raise KernelError(f"{nh} query heads do not divide into {nkv} key/value heads")
-    if d > 512:
-        raise KernelError(f"head size {d} is larger than the plain attention kernel's limit of 512")
+    if max(d, dv) > 1024:
+        raise KernelError(f"head size {max(d, dv)} is larger than the plain attention kernel's limit of 1024")
     _ok(kernels_lib().xb_attention_plain(
-        dtype_code(q.dtype), out.data_ptr(), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(),
-        req_of_token.data_ptr(), block_table.data_ptr(), int(table_stride), T, nh, nkv, d, page_size, num_pages,
-        int(window or 0), float(scale), err.data_ptr(), _stream()), "attention_plain")
+        dtype_code(q.dtype), out.data_ptr(), q.data_ptr(), nh * d, d, k_cache.data_ptr(), v_cache.data_ptr(), d, v_stride,
+        _ptr(sink), positions.data_ptr(), req_of_token.data_ptr(), block_table.data_ptr(), int(table_stride), T, nh, nkv, d,
+        dv, page_size, num_pages, int(window or 0), float(scale), err.data_ptr(), _stream()), "attention_plain")
 
 
-def swiglu(out, gate_up):
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def swiglu(out, gate_up, activation: str = "silu"):
+    """out[t, i] = act(gate_up[t, i]) * gate_up[t, I + i]; ``activation``: "silu" or "gelu_tanh"."""
+    act = ACTIVATIONS[activation]
     T, two_i = gate_up.shape
     _need(gate_up, "gate_up", None, (T, two_i))
     _need(out, "out", gate_up.dtype, (T, two_i // 2))
     if vectorized and gate_up.dtype == torch.bfloat16 and two_i % 16 == 0:
         if T >= many_rows:
-            _ok(kernels_lib().xb_swiglu_rows_bf16(out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, _stream()), "swiglu_rows_bf16")
+            _ok(kernels_lib().xb_swiglu_rows_bf16(out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, act, _stream()), "swiglu_rows_bf16")
             return
-        _ok(kernels_lib().xb_swiglu_bf16(out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, _stream()), "swiglu_bf16")
+        _ok(kernels_lib().xb_swiglu_bf16(out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, act, _stream()), "swiglu_bf16")
         return
-    _ok(kernels_lib().xb_swiglu(dtype_code(gate_up.dtype), out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, _stream()), "swiglu")
+    _ok(kernels_lib().xb_swiglu(dtype_code(gate_up.dtype), out.data_ptr(), gate_up.data_ptr(), T, two_i // 2, act, _stream()), "swiglu")
 
 
 def widen_bf16(out, x):
@@ -608,11 +668,11 @@ def attn_prefill_tc(out, q, k_cache, v_cache, q_start, start_pos, block_table, t
 
 # ---- attention with talking heads and a sink; gated recurrence; polynomial activation; table experts ----
 def qkv_prepare(q_out, k_cache, v_cache, qkv, q_w, k_w, inv_freq, positions, req_of_token, block_table, table_stride,
-                nh, nkv, d, dv, rot, interleaved, norm_mode, eps, write_kv, err):
+                nh, nkv, d, dv, rot, interleaved, norm_mode, eps, write_kv, err, rot_magnitude: float = 1.0):
     """Per q/k head of the packed ``qkv`` rows ``[heads*d | kv_heads*d | kv_heads*dv]``: norm over the head
     (``norm_mode`` 1: before the rotation, 2: after it, 0: none; weight ``q_w`` / ``k_w`` or none), rotation of
     the first ``rot`` channels by ``position * inv_freq`` (float32 angles formed in the kernel; ``inv_freq`` None:
-    no rotation); q to ``q_out``, k and v into their pages."""
+    no rotation; cos and sin are multiplied by ``rot_magnitude``); q to ``q_out``, k and v into their pages."""
     T = qkv.shape[0]
     _need(qkv, "qkv", None, (T, (nh + nkv) * d + nkv * dv))
     _need(q_out, "q_out", qkv.dtype, (T, nh, d))
@@ -630,7 +690,7 @@ def qkv_prepare(q_out, k_cache, v_cache, qkv, q_w, k_w, inv_freq, positions, req
         dtype_code(qkv.dtype), q_out.data_ptr(), _ptr(k_cache), _ptr(v_cache), qkv.data_ptr(), _ptr(q_w), _ptr(k_w),
         _ptr(inv_freq), positions.data_ptr(), req_of_token.data_ptr(), block_table.data_ptr(), int(table_stride), T, nh, nkv,
         d, dv, int(rot if inv_freq is not None else 0), int(bool(interleaved)), int(norm_mode), page_size, num_pages,
-        float(eps), int(bool(write_kv)), err.data_ptr(), _stream()), "qkv_prepare")
+        float(eps), int(bool(write_kv)), float(rot_magnitude), err.data_ptr(), _stream()), "qkv_prepare")
 
 
 def attn_talking_tile(nh: int, d: int, dv: int, want: int) -> int:
@@ -812,3 +872,58 @@ def expert_combine(out, y, inv, top: int):
     _need(out, "out", None, (T, N))
     _ok(kernels_lib().xb_expert_combine(dtype_code(out.dtype), out.data_ptr(), y.data_ptr(), inv.data_ptr(), T, int(top), N,
                                         _stream()), "expert_combine")
+
+
+# ---- attention over a cached latent ---------------------------------------------------------------------------------
+def latent_prepare(q_abs, cache, proj, q_off, kv_off, q_lat, norm_w, inv_freq, positions, req_of_token, block_table,
+                   table_stride, nh, d, rd, rank, rot, eps, rot_magnitude, err):
+    """Per token of the packed projection ``proj``: the query of every head as ``q_abs[t, h] = [q_lat[h, t] | rotated
+    rd channels]`` (``q_lat`` ``[heads, T, rank]``: the plain query part carried into the latent space), and, with
+    ``kv_off`` >= 0, the cached row ``[RMS-normed rank channels * norm_w | rotated rd channels]`` into its page
+    (``cache`` ``[page, slot, rank + rd]``).  Rotation: pairs (2i, 2i + 1) of the first ``rot`` channels by
+    ``position * inv_freq[i]``, cos and sin times ``rot_magnitude``."""
+    T = proj.shape[0]
+    _need(proj, "proj", None, (T, None))
+    _need(q_abs, "q_abs", proj.dtype, (T, nh, rank + rd))
+    _need(q_lat, "q_lat", proj.dtype, (nh, T, rank))
+    _need(cache, "cache", proj.dtype, (None, None, rank + rd))
+    _need(inv_freq, "inv_freq", torch.float32, (rot // 2,))
+    if kv_off >= 0:
+        _need(norm_w, "norm_w", torch.float32, (rank,))
+        if kv_off + rank + rd > proj.shape[1]:
+            raise KernelError("the latent part lies outside the projection's rows")
+    if q_off + nh * (d + rd) > proj.shape[1]:
+        raise KernelError("the queries lie outside the projection's rows")
+    _ok(kernels_lib().xb_latent_prepare(
+        dtype_code(proj.dtype), q_abs.data_ptr(), cache.data_ptr(), proj.data_ptr(), proj.shape[1], int(q_off), int(kv_off),
+        q_lat.data_ptr(), rank, T * rank, _ptr(norm_w), inv_freq.data_ptr(), positions.data_ptr(), req_of_token.data_ptr(),
+        block_table.data_ptr(), int(table_stride), T, nh, d, rd, rank, int(rot), cache.shape[1], cache.shape[0], float(eps),
+        float(rot_magnitude), err.data_ptr(), _stream()), "latent_prepare")
+
+
+def gate_sigmoid(out, heads, gate):
+    """out[t, h, :] = heads[h, t, :] * sigmoid(gate[t, h, :]); ``gate`` may be a column range of a wider tensor."""
+    nh, T, dv = heads.shape
+    _need(heads, "heads", None, (nh, T, dv))
+    _need(out, "out", heads.dtype, (T, nh * dv))
+    if (gate.dtype != heads.dtype or tuple(gate.shape) != (T, nh * dv) or gate.stride(1) != 1 or not gate.is_cuda):
+        raise KernelError("gate must be a [T, heads * dv] view with unit column stride in the heads' type")
+    _ok(kernels_lib().xb_gate_sigmoid(dtype_code(heads.dtype), out.data_ptr(), heads.data_ptr(), dv, T * dv, gate.data_ptr(),
+                                      gate.stride(0), T, nh, dv, _stream()), "gate_sigmoid")
+
+
+def gemm_batched_plain(out, a, w):
+    """out[b, m, n] = sum_k a[b, m, k] * w[b, n, k] with float32 FMA accumulation.  ``a`` ``[B, M, K]`` and ``out``
+    ``[B, M, N]`` may be any views whose last stride is 1; ``w`` ``[B, N, K]`` any view with one unit stride among its
+    last two."""
+    B, M, K = a.shape
+    N = w.shape[1]
+    if tuple(w.shape) != (B, N, K) or tuple(out.shape) != (B, M, N):
+        raise KernelError(f"batched product: a {tuple(a.shape)}, w {tuple(w.shape)}, out {tuple(out.shape)} do not fit")
+    if not (a.is_cuda and w.is_cuda and out.is_cuda) or a.dtype != w.dtype or a.dtype != out.dtype:
+        raise KernelError("batched product: CUDA tensors of one type are needed")
+    if a.stride(2) != 1 or out.stride(2) != 1 or 1 not in (w.stride(1), w.stride(2)):
+        raise KernelError("batched product: a and out need a unit last stride, w a unit stride in one of its last two")
+    _ok(kernels_lib().xb_gemm_batched_plain(dtype_code(a.dtype), out.data_ptr(), a.data_ptr(), w.data_ptr(), B, M, N, K,
+                                            a.stride(0), a.stride(1), w.stride(0), w.stride(1), w.stride(2), out.stride(0),
+                                            out.stride(1), _stream()), "gemm_batched_plain")

@@ -14,7 +14,7 @@ import torch
 from .. import kernels, tracing
 from ..config.plan import ModelPlan
 from ..parts import Block, LayerCache, StepContext, build_part, part_class
-from ..parts.block import Stream
+from ..parts.block import Stream, fused_norm
 from ..parts.linear import linear
 from ..weights.loader import WeightSpec, WeightStore
 
@@ -121,7 +121,7 @@ class DecoderModel:
         if trace:
             tracing.push("head")
         y = ws.get("model.final", (R, H), self.dtype)
-        self.final_norm.forward(y, stream.x, ctx, branch=stream.settle(keep_last=True), rows=ctx.logit_rows)
+        fused_norm(self.final_norm, y, stream.x, ctx, stream.settle(ctx, keep_last=True), rows=ctx.logit_rows)
         linear(logits, y, self.head, ctx.err)
         if self.plan.logit_scale is not None or self.plan.logit_softcap is not None:
             kernels.logits_post(logits, self.plan.logit_scale, self.plan.logit_softcap)

@@ -88,22 +88,22 @@ def _declare_kernels(lib):
     _sig(lib, "xb_embedding", I, [I, P, P, P, P, I, I, I, I, F, P, P])
     _sig(lib, "xb_logits_post", I, [P, L, F, F, P])
     _sig(lib, "xb_rmsnorm", I, [I, P, P, P, P, P, P, I, I, I, F, F, P, P])
-    _sig(lib, "xb_add", I, [I, P, P, P, L, P])
+    _sig(lib, "xb_add", I, [I, P, P, P, L, F, P])
     _sig(lib, "xb_gemm_plain", I, [I, I, I, P, P, P, I, I, I, P])
     _sig(lib, "xb_rope_table", I, [P, P, P, I, I, P])
     _sig(lib, "xb_qk_norm_rope_write", I,
          [I, P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P])
-    _sig(lib, "xb_attention_plain", I, [I, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, P])
-    _sig(lib, "xb_swiglu", I, [I, P, P, I, I, P])
+    _sig(lib, "xb_attention_plain", I, [I, P, P, L, L, P, P, I, I, P, P, P, P, I, I, I, I, I, I, I, I, I, F, P, P])
+    _sig(lib, "xb_swiglu", I, [I, P, P, I, I, I, P])
     _sig(lib, "xb_widen_bf16", I, [P, P, L, P])
     _sig(lib, "xb_sample", I, [P, P, P, P, I, I, I, I, P, P, P])
     _sig(lib, "xb_sample_scratch_bytes", c_longlong, [I])
     _sig(lib, "xb_sample_params_size", I, [])
     _sig(lib, "xb_rmsnorm_bf16", I, [P, P, P, P, P, P, I, I, I, F, F, P, P])
-    _sig(lib, "xb_swiglu_bf16", I, [P, P, I, I, P])
+    _sig(lib, "xb_swiglu_bf16", I, [P, P, I, I, I, P])
     _sig(lib, "xb_qk_norm_rope_write_bf16", I,
          [P, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, F, I, P, P])
-    _sig(lib, "xb_swiglu_rows_bf16", I, [P, P, I, I, P])
+    _sig(lib, "xb_swiglu_rows_bf16", I, [P, P, I, I, I, P])
     _sig(lib, "xb_attn_prefill_tc", I, [P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, F, P, I, P, P])
     _sig(lib, "xb_gemm_skinny_tc", I, [P, I, P, P, I, I, I, I, P, P])
     _sig(lib, "xb_gemm_skinny_swiglu", I, [P, P, P, I, I, I, I, P, P])
@@ -116,8 +116,12 @@ def _declare_kernels(lib):
     _sig(lib, "xb_attn_decode_plan", I, [P, P, P, P, I, I, I, I, I, I, I, I, P, P])
     _sig(lib, "xb_embedding_f32", I, [I, P, P, P, P, I, I, I, I, F, P, P])
     _sig(lib, "xb_rmsnorm_f32", I, [I, I, P, P, P, P, P, P, I, I, I, F, F, P, P])
-    _sig(lib, "xb_add_f32", I, [I, P, P, P, L, P])
-    _sig(lib, "xb_qkv_prepare", I, [I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, P, P])
+    _sig(lib, "xb_add_f32", I, [I, P, P, P, L, F, P])
+    _sig(lib, "xb_qkv_prepare", I, [I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, F, P, P])
+    _sig(lib, "xb_dyt_norm", I, [I, I, I, P, P, P, P, P, P, P, P, F, P, P, P, I, I, I, P, P])
+    _sig(lib, "xb_latent_prepare", I, [I, P, P, P, L, I, I, P, L, L, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, P, P])
+    _sig(lib, "xb_gate_sigmoid", I, [I, P, P, L, L, P, L, I, I, I, P])
+    _sig(lib, "xb_gemm_batched_plain", I, [I, P, P, P, I, I, I, I, L, L, L, L, L, L, L, P])
     _sig(lib, "xb_attn_talking_tile", I, [I, I, I, I])
     _sig(lib, "xb_attn_talking", I, [I, P, I, P, P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, I, F, I, F, I, I, P, P, P, P])
     _sig(lib, "xb_attn_talking_mma_tile", I, [I, I, I, I, I])

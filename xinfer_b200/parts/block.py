@@ -27,21 +27,67 @@ from .base import LayerCache, Part, StepContext, build_part, part_class
 _FAMILY = {"norm": "norm", "mixer": "mixer", "feed_forward": "feed_forward"}
 
 
+class Addend:
+    """A value that waits to be added into another: ``scale * norm(t)``, where ``norm`` (a norm part, or None) has
+    not been carried out yet - the kernel that forms the sum may do it, if its kind offers that."""
+
+    __slots__ = ("t", "scale", "norm")
+
+    def __init__(self, t: torch.Tensor, scale: float = 1.0, norm=None):
+        self.t = t
+        self.scale = scale
+        self.norm = norm
+
+    def plain(self, ctx) -> torch.Tensor:
+        """The tensor with its norm carried out (in place: the unnormed value is read by nobody else)."""
+        if self.norm is not None:
+            self.norm.forward(self.t, self.t, ctx)
+            self.norm = None
+        return self.t
+
+
+def _add_into(dst: torch.Tensor, a: Addend, ctx) -> None:
+    kernels.add(dst, dst, a.plain(ctx), a.scale)
+
+
+def fused_norm(part, out, src, ctx, last: Optional[Addend], rows=None):
+    """``out = part(src + last)`` in one kernel where the norm's kind takes what the addend needs (a scale, a norm of
+    its own of the same kind); the sum is stored back into ``src`` unless rows are gathered."""
+    if last is None:
+        return part.forward(out, src, ctx, rows=rows) if rows is not None else part.forward(out, src, ctx)
+    kw = {}
+    if last.norm is not None:
+        if getattr(part, "takes_branch_norm", False) and type(last.norm) is type(part):
+            kw["branch_norm"] = last.norm
+        else:
+            last.plain(ctx)
+    if last.scale != 1.0:
+        if getattr(part, "takes_branch_scale", False):
+            kw["branch_scale"] = last.scale
+        else:
+            # the norm cannot scale its branch: the sum is formed by an addition kernel first
+            _add_into(src, last, ctx)
+            return part.forward(out, src, ctx, rows=rows) if rows is not None else part.forward(out, src, ctx)
+    if rows is not None:
+        return part.forward(out, src, ctx, branch=last.t, rows=rows, **kw)
+    return part.forward(out, src, ctx, branch=last.t, sum_out=src, **kw)
+
+
 class Stream:
     """The residual stream between blocks: its tensor and the branches still to be added to it."""
 
     __slots__ = ("x", "pending")
 
-    def __init__(self, x: torch.Tensor, pending: Optional[List[torch.Tensor]] = None):
+    def __init__(self, x: torch.Tensor, pending: Optional[List[Addend]] = None):
         self.x = x
-        self.pending: List[torch.Tensor] = pending or []
+        self.pending: List[Addend] = pending or []
 
-    def settle(self, keep_last: bool = False) -> Optional[torch.Tensor]:
+    def settle(self, ctx, keep_last: bool = False) -> Optional[Addend]:
         """Carry out the waiting additions; with ``keep_last`` the last one is handed back for a
         norm kernel to fuse."""
         last = self.pending.pop() if (keep_last and self.pending) else None
         for b in self.pending:
-            kernels.add(self.x, self.x, b)
+            _add_into(self.x, b, ctx)
         self.pending = []
         return last
 
@@ -82,16 +128,19 @@ class Block:
     def forward(self, stream: Stream, ctx: StepContext, cache: Optional[LayerCache], state, writes_cache: bool) -> Stream:
         """Runs the program on the residual stream; returns the stream with the additions that
         still wait."""
-        T, H = stream.x.shape
         ws = ctx.workspace
         vals: Dict[str, torch.Tensor] = {"x": stream.x}
-        waiting: Dict[str, List[torch.Tensor]] = {"x": stream.pending}
+        waiting: Dict[str, List[Addend]] = {"x": stream.pending}
+        lazy: Dict[str, Part] = {}      # block-local values whose norm waits for the addition that follows it
 
         def read(name: str) -> torch.Tensor:
             """The value with every addition into it carried out."""
             t = vals[name]
+            if name in lazy:
+                part = lazy.pop(name)
+                part.forward(t, t, ctx)
             for b in waiting.pop(name, ()):
-                kernels.add(t, t, b)
+                _add_into(t, b, ctx)
             return t
 
         def settle_all() -> None:
@@ -99,26 +148,38 @@ class Block:
             for name in list(waiting):
                 read(name)
 
-        for o in self.spec.program:
+        program = self.spec.program
+        for idx, o in enumerate(program):
             if o.op == "add":
-                waiting.setdefault(o.dst, []).append(read(o.src))
+                if o.src in lazy and not waiting.get(o.src):
+                    waiting.setdefault(o.dst, []).append(Addend(vals[o.src], o.scale, lazy.pop(o.src)))
+                else:
+                    waiting.setdefault(o.dst, []).append(Addend(read(o.src), o.scale))
                 continue
             part = self.parts[(o.op, o.name)]
             if o.op == "norm":
+                nxt = program[idx + 1] if idx + 1 < len(program) else None
+                if (o.src == o.dst and o.src != "x" and o.src not in lazy and not waiting.get(o.src)
+                        and getattr(part, "takes_branch_norm", False)
+                        and nxt is not None and nxt.op == "add" and nxt.src == o.dst):
+                    # a norm in place of a block-local value that is only added into another value next: it
+                    # waits, and the kernel that forms that sum carries it out
+                    lazy[o.dst] = part
+                    continue
                 src = vals[o.src]
+                if o.src in lazy:
+                    read(o.src)
                 adds = waiting.pop(o.src, [])
                 for b in adds[:-1]:
-                    kernels.add(src, src, b)
+                    _add_into(src, b, ctx)
+                last = adds[-1] if adds else None
                 out = ws.get("block." + o.dst, tuple(src.shape), self.dtype)
-                if any(out.data_ptr() == t.data_ptr() for t in (src, *adds)):
+                if any(out.data_ptr() == t.data_ptr() for t in (src, *([last.t] if last else []))):
                     # a norm back into its own input (or over its addend) gets a buffer of its own
                     out = ws.get("block." + o.dst + "'", tuple(src.shape), self.dtype)
                 if tracing.ENABLED:
                     tracing.push("norm")
-                if adds:
-                    part.forward(out, src, ctx, branch=adds[-1], sum_out=src)
-                else:
-                    part.forward(out, src, ctx)
+                fused_norm(part, out, src, ctx, last)
                 if tracing.ENABLED:
                     tracing.pop()
             else:
@@ -132,6 +193,7 @@ class Block:
                 if tracing.ENABLED:
                     tracing.pop()
             waiting.pop(o.dst, None)      # additions that waited for the value this one replaces are void
+            lazy.pop(o.dst, None)
             vals[o.dst] = out
         # additions into block-local values that nothing read are void; the stream's wait for its next reader
         return Stream(vals["x"], waiting.get("x", []))

@@ -8,7 +8,7 @@ from typing import List
 import torch
 
 from .. import kernels
-from ..config.plan import NormSpec
+from ..config.plan import DynamicTanhSpec, NormSpec
 from ..weights.loader import WeightSpec
 from .base import Norm, register_norm
 
@@ -35,4 +35,39 @@ class RMSNorm(Norm):
         return out
 
 
+class DynamicTanh(Norm):
+    """``y = tanh(alpha * x) * w + b``: no mean, no variance, every element alone.  Being elementwise, it can
+    take the whole residual step around it into its kernel: a branch that is scaled (``branch_scale``) and first
+    passed through a Dynamic Tanh of its own (``branch_norm``) before it is added."""
+
+    kind = "dynamic_tanh"
+    graph_safe = True
+    takes_branch_scale = True
+    takes_branch_norm = True
+
+    def __init__(self, spec: DynamicTanhSpec, prefix: str, dtype, device):
+        super().__init__(spec, prefix, dtype, device)
+        self.weight = self.bias = self.alpha = None
+
+    @classmethod
+    def weight_specs(cls, spec: DynamicTanhSpec, prefix: str) -> List[WeightSpec]:
+        return [WeightSpec(prefix + spec.weight_name, (spec.dim,), "norm"),
+                WeightSpec(prefix + spec.bias_name, (spec.dim,), "around_zero"),
+                WeightSpec(prefix + spec.alpha_name, (), "norm")]
+
+    def load(self, store) -> None:
+        def f32(name):
+            return store.get(self.prefix + name, self.device, torch.float32).float().contiguous()
+        self.weight, self.bias, self.alpha = f32(self.spec.weight_name), f32(self.spec.bias_name), f32(self.spec.alpha_name)
+
+    def params(self):
+        return (self.alpha, self.weight, self.bias)
+
+    def forward(self, out, x, ctx, branch=None, sum_out=None, rows=None, branch_scale: float = 1.0, branch_norm=None):
+        kernels.dyt_norm(out, x, self.alpha, self.weight, self.bias, ctx.err, branch=branch, branch_scale=branch_scale,
+                         branch_norm=branch_norm.params() if branch_norm is not None else None, sum_out=sum_out, rows=rows)
+        return out
+
+
 register_norm("rmsnorm", RMSNorm)
+register_norm("dynamic_tanh", DynamicTanh)

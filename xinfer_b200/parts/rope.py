@@ -11,7 +11,7 @@ import numpy as np
 import torch
 
 from .. import kernels
-from ..config.plan import RopeSpec
+from ..config.plan import RopeSpec, YarnScaling
 from .base import PositionEncoding, register_position_encoding
 
 
@@ -36,6 +36,15 @@ def inv_frequencies(theta: float, rotary_dim: int, scaling=None, rounded_once: b
     f = np.power(np.float64(theta), -j / np.float64(rotary_dim))
     if scaling is None:
         return f.astype(np.float32)
+    if isinstance(scaling, YarnScaling):
+        # pairs that make many turns within the original length keep their frequency, pairs that make few are
+        # slowed by the factor, with a linear ramp over the pair index between the two
+        def pair_at(turns: float) -> float:
+            return rotary_dim * np.log(scaling.original / (2.0 * np.pi * turns)) / (2.0 * np.log(np.float64(theta)))
+        lo = max(np.floor(pair_at(scaling.fast)), 0.0)
+        hi = min(np.ceil(pair_at(scaling.slow)), rotary_dim - 1.0)
+        ramp = np.clip((j / 2.0 - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return (f / scaling.factor * ramp + f * (1.0 - ramp)).astype(np.float32)
     wavelength = 2.0 * np.pi / f
     s = (scaling.original / wavelength - scaling.low) / (scaling.high - scaling.low)
     blended = (1.0 - s) * f / scaling.factor + s * f
@@ -73,13 +82,16 @@ class Rope(PositionEncoding):
             raise ValueError("this rotary encoding keeps no tables (its spec says tables=False); use frequencies()")
         if self._tables is None:
             s = self.spec
-            key = (str(self.device), s.theta, s.rotary_dim, s.max_positions, s.scaling)
+            key = (str(self.device), s.theta, s.rotary_dim, s.max_positions, s.scaling, s.magnitude)
             if key not in _TABLE_CACHE:  # layers with the same constants share one table
                 half = s.rotary_dim // 2
                 inv = torch.from_numpy(inv_frequencies(s.theta, s.rotary_dim, s.scaling)).to(self.device)
                 cos = torch.empty((s.max_positions, half), dtype=torch.float32, device=self.device)
                 sin = torch.empty_like(cos)
                 kernels.rope_table(cos, sin, inv)
+                if s.magnitude != 1.0:
+                    cos.mul_(s.magnitude)
+                    sin.mul_(s.magnitude)
                 _TABLE_CACHE[key] = (cos, sin)
             cos, sin = _TABLE_CACHE[key]
             self._tables = RotaryTables(cos, sin, s.rotary_dim, s.layout == "interleaved")

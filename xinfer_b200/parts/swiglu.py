@@ -1,5 +1,6 @@
-"""SiLU-gated feed-forward: ``down( silu(gate(x)) * up(x) )`` with gate and up concatenated into
-one projection at load (src/models/layers/mlp.rs:447-466, forward :613-697), no biases."""
+"""Gated feed-forward: ``down( act(gate(x)) * up(x) )`` with gate and up concatenated into
+one projection at load (src/models/layers/mlp.rs:447-466, forward :613-697), no biases.  ``act`` is SiLU
+(the reference's) or the tanh form of GELU; the three tensors' names may be given by the spec."""
 from __future__ import annotations
 
 from typing import List
@@ -14,43 +15,50 @@ from . import gemm_backend
 from .linear import linear
 
 
+_DEFAULT_NAMES = ("gate_proj.weight", "up_proj.weight", "down_proj.weight")
+
+
 class SwiGLU(FeedForward):
     kind = "swiglu"
     graph_safe = True
 
     def __init__(self, spec: FeedForwardSpec, prefix: str, dtype, device):
         super().__init__(spec, prefix, dtype, device)
-        if spec.activation != "silu":
-            raise ValueError(f"the gated feed-forward supports 'silu', not '{spec.activation}'")
+        if spec.activation not in kernels.ACTIVATIONS:
+            raise ValueError(f"the gated feed-forward supports {', '.join(sorted(kernels.ACTIVATIONS))}, not '{spec.activation}'")
+        self.names = tuple(spec.names) if spec.names else _DEFAULT_NAMES
         self.w_gate_up = self.w_down = None
 
     @classmethod
     def weight_specs(cls, spec: FeedForwardSpec, prefix: str) -> List[WeightSpec]:
         p = prefix
+        n = tuple(spec.names) if spec.names else _DEFAULT_NAMES
         return [
-            WeightSpec(p + "gate_proj.weight", (spec.intermediate, spec.hidden)),
-            WeightSpec(p + "up_proj.weight", (spec.intermediate, spec.hidden)),
-            WeightSpec(p + "down_proj.weight", (spec.hidden, spec.intermediate)),
+            WeightSpec(p + n[0], (spec.intermediate, spec.hidden)),
+            WeightSpec(p + n[1], (spec.intermediate, spec.hidden)),
+            WeightSpec(p + n[2], (spec.hidden, spec.intermediate)),
         ]
 
     def load(self, store) -> None:
         p = self.prefix
-        g = store.get(p + "gate_proj.weight", self.device, self.dtype, operand=True)
-        u = store.get(p + "up_proj.weight", self.device, self.dtype, operand=True)
+        g = store.get(p + self.names[0], self.device, self.dtype, operand=True)
+        u = store.get(p + self.names[1], self.device, self.dtype, operand=True)
         self.w_gate_up = torch.cat([g, u], dim=0).contiguous()
         del g, u
-        self.w_down = store.get(p + "down_proj.weight", self.device, self.dtype, operand=True)
+        self.w_down = store.get(p + self.names[2], self.device, self.dtype, operand=True)
 
     def forward(self, x, ctx: StepContext):
         s = self.spec
         T = x.shape[0]
         ws = ctx.workspace
         act = ws.get("ffn.act", (T, s.intermediate), self.dtype)
-        if not gemm_backend.try_fused_gate(act, x, self.w_gate_up, ctx.err):
+        if s.activation != "silu" or not gemm_backend.try_fused_gate(act, x, self.w_gate_up, ctx.err):
             gu = ws.get("ffn.gate_up", (T, 2 * s.intermediate), self.dtype)
             linear(gu, x, self.w_gate_up, ctx.err)
-            kernels.swiglu(act, gu)
-        out = ws.get("ffn.out", (T, s.hidden), self.dtype)
+            kernels.swiglu(act, gu, s.activation)
+        # the result leaves in the type the residual stream takes its branches in (float32 accumulators unrounded
+        # where the stream is float32)
+        out = ws.get("ffn.out", (T, s.hidden), ctx.branch_dtype or self.dtype)
         linear(out, act, self.w_down, ctx.err)
         return out
 

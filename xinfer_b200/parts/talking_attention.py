@@ -102,7 +102,7 @@ class TalkingAttention(Mixer):
                             self.position.frequencies() if rope is not None else None, ctx.positions, ctx.req_of_token,
                             table, stride, nh, nkv, d, dv, rope.rotary_dim if rope is not None else 0,
                             rope is not None and rope.layout == "interleaved", norm_mode, s.qk_norm_eps, writes_cache,
-                            ctx.err)
+                            ctx.err, rot_magnitude=rope.magnitude if rope is not None else 1.0)
         # queries per block: the longest portion decides (a step of single tokens takes one query per block
         # and cuts the keys instead); a replayed step must not look at its actual lengths
         single = ctx.all_single or ctx.fixed_shapes
