@@ -7,6 +7,7 @@
     python bench.py --kernels --attn 16,8,64                # the attention kernels at another head layout
     python bench.py --ablate                                # a decode step with one kind of kernel left out at a time
     python bench.py --compare tidarax [--size 1k|4k]        # the Tidarax design beside Qwen3 at equal layer sizes
+    python bench.py --compare dufitar [--size 1k|4k]        # the Dufitar design beside Qwen3 at equal layer sizes
 
 Prints ONE JSON line.  ``value`` is decoded tokens per second at batch 8 and the context length
 of the configuration (a "step" is one decode step of the whole batch), timed on the device with
@@ -224,10 +225,37 @@ def tidarax_config(z: dict, layers: int, vocab: int) -> dict:
                 layers=[dict(type="parallel", mixer=mixer, mlp=dense if i % 2 == 0 else moe) for i in range(layers)])
 
 
+# The latent layers of --compare dufitar: what a token leaves in the cache, and the rotated part of a head.
+LATENT_SIZES = {"1k": dict(kv_rank=256, rot_dim=32), "4k": dict(kv_rank=512, rot_dim=64)}
+# windows of --compare dufitar: wider than the benchmark's context, so that its attention does the work of
+# the Qwen3 model's (which sees every earlier key)
+COMPARE_WINDOW = 4096
+
+
+def dufitar_config(z: dict, lat: dict, layers: int, vocab: int) -> dict:
+    d = z["head_dim"]
+    attn = dict(type="attention", mlp=dict(kind="dense", ff=z["intermediate"]),
+                mixer=dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=d, vdim=d, scale=d ** -0.5, mask=dict(size=COMPARE_WINDOW),
+                           rot=dict(dims=d // 2, base=500000.0, scaling=dict(factor=4.0, original=8192, fast=32.0, slow=1.0))))
+
+    def latent(kv_from=None):
+        m = dict(heads=z["heads"], dim=d, rot_dim=lat["rot_dim"], vdim=d, kv_rank=lat["kv_rank"],
+                 scale=(d + lat["rot_dim"]) ** -0.5, mask=dict(size=COMPARE_WINDOW), rot=dict(dims=lat["rot_dim"], base=250000.0))
+        if kv_from is not None:
+            m["kv_from"] = kv_from
+        return dict(type="latent_attention", mixer=m, mlp=dict(kind="dense", ff=z["intermediate"]))
+
+    out = []
+    for i in range(layers):      # attention, latent, attention, latent reading the rows of the latent layer before it
+        out.append(attn if i % 2 == 0 else latent(i - 2 if i % 4 == 3 else None))
+    return dict(architecture="Dufitar", vocab=vocab, width=z["hidden"], norm=dict(eps=1e-6), residual_mult=0.7,
+                embedding=dict(scale=2.0), layers=out)
+
+
 def compare(args) -> int:
-    """Prefill and decode throughput of a Tidarax model and of a Qwen3 model of the same layer sizes (random
-    weights, `--layers` layers each, default 4), then the Tidarax kernels one by one beside their like kernels.
-    One JSON line per model and per kernel."""
+    """Prefill and decode throughput of a model of the named design and of a Qwen3 model of the same layer sizes
+    (random weights, `--layers` layers each, default 4), then the design's kernels one by one beside their like
+    kernels.  One JSON line per model and per kernel."""
     import numpy as np
     import torch
     from xinfer_b200 import measure
@@ -236,7 +264,8 @@ def compare(args) -> int:
     z = COMPARE_SIZES[args.size]
     L, V, B, ctx_len = args.layers or 4, 32000, args.batch, 2048
     models = {
-        "Tidarax": tidarax_config(z, L, V),
+        ("Tidarax" if args.compare == "tidarax" else "Dufitar"):
+            tidarax_config(z, L, V) if args.compare == "tidarax" else dufitar_config(z, LATENT_SIZES[args.size], L, V),
         "Qwen3": dict(CONFIG, vocab_size=V, hidden_size=z["hidden"], intermediate_size=z["intermediate"], num_hidden_layers=L,
                       num_attention_heads=z["heads"], num_key_value_heads=z["kv_heads"], head_dim=z["head_dim"]),
     }
@@ -285,9 +314,17 @@ def compare(args) -> int:
                           "dtype": "bf16", "data": "synthetic (random weights, seeded uniform token ids)"}), flush=True)
         del runner
         torch.cuda.empty_cache()
-    for rec in measure.tidarax_kernels(hidden=z["hidden"], heads=z["heads"], kv_heads=z["kv_heads"], head_dim=z["head_dim"],
-                                       intermediate=z["intermediate"], rec_width=z["hidden"], experts=z["experts"],
-                                       expert_ff=z["expert_ff"], top=z["top"], hbm_gbs=pk["hbm_gbs"], peak_tflops=pk["bf16_tflops"]):
+    if args.compare == "dufitar":
+        lat = LATENT_SIZES[args.size]
+        records = measure.dufitar_kernels(hidden=z["hidden"], heads=z["heads"], kv_heads=z["kv_heads"], head_dim=z["head_dim"],
+                                          intermediate=z["intermediate"], kv_rank=lat["kv_rank"], rot_dim=lat["rot_dim"],
+                                          hbm_gbs=pk["hbm_gbs"], peak_tflops=pk["bf16_tflops"])
+    else:
+        records = measure.tidarax_kernels(hidden=z["hidden"], heads=z["heads"], kv_heads=z["kv_heads"], head_dim=z["head_dim"],
+                                          intermediate=z["intermediate"], rec_width=z["hidden"], experts=z["experts"],
+                                          expert_ff=z["expert_ff"], top=z["top"], hbm_gbs=pk["hbm_gbs"],
+                                          peak_tflops=pk["bf16_tflops"])
+    for rec in records:
         print(json.dumps(dict(rec, size=args.size)), flush=True)
     return 0
 
@@ -315,7 +352,7 @@ def main() -> int:
                     help="with --kernels: the attention kernels alone at this head layout, over short and long contexts")
     ap.add_argument("--case", default="", metavar="decode:BATCHxCONTEXT | prefill:CACHED+NEW",
                     help="with --kernels --attn: this one case instead of the standard ones")
-    ap.add_argument("--compare", default="", choices=["", "tidarax"],
+    ap.add_argument("--compare", default="", choices=["", "tidarax", "dufitar"],
                     help="instead of the step benchmark: prefill and decode throughput of this design beside Qwen3 at equal "
                          "layer sizes, and its kernels beside their like kernels; one JSON line each")
     ap.add_argument("--size", default="4k", choices=sorted(COMPARE_SIZES), help="layer sizes of --compare")

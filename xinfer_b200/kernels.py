@@ -901,6 +901,38 @@ def latent_prepare(q_abs, cache, proj, q_off, kv_off, q_lat, norm_w, inv_freq, p
         float(rot_magnitude), err.data_ptr(), _stream()), "latent_prepare")
 
 
+def attn_latent_mma_takes(dk: int, rank: int) -> bool:
+    """Whether the tensor-core attention over latent rows takes these sizes (bfloat16 only)."""
+    return bool(kernels_lib().xb_attn_latent_mma_takes(int(dk), int(rank)))
+
+
+def attn_latent_mma(out, q, cache, q_start, start_pos, num_entries, block_table, table_stride, window, scale, sink, err, *,
+                    row_groups: int = 2, parts: int = 1, part_o=None, part_ml=None):
+    """Attention of every (token, head) row of ``q`` ``[T, heads, dk]`` over its request's cached rows
+    (``cache`` ``[page, slot, dk]``; the first ``rank = out.shape[-1]`` channels of a row are its value), bfloat16 on
+    tensor cores with float32 scores, softmax and sums.  ``sink`` (float32 per head or None): one more softmax entry
+    of that score without a value.  ``row_groups``: 16-row groups per block (1 or 2).  ``parts`` > 1: every row's key
+    tiles are dealt out to that many blocks and merged through ``part_o`` / ``part_ml`` (float32, T*heads*parts*rank
+    and T*heads*parts*2 elements)."""
+    T, nh, dk = q.shape
+    _need(q, "q", torch.bfloat16, (T, nh, dk))
+    rank = out.shape[-1]
+    _need(out, "out", torch.bfloat16, (T, nh, rank))
+    _need(cache, "cache", torch.bfloat16, (None, None, dk))
+    if sink is not None:
+        _need(sink, "sink", torch.float32, (nh,))
+    if parts > 1:
+        _need(part_o, "part_o", torch.float32)
+        _need(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < T * nh * parts * rank or part_ml.numel() < T * nh * parts * 2:
+            raise KernelError("attention scratch buffers are too small for the number of key ranges")
+    _ok(kernels_lib().xb_attn_latent_mma(
+        out.data_ptr(), q.data_ptr(), cache.data_ptr(), q_start.data_ptr(), start_pos.data_ptr(), int(num_entries),
+        block_table.data_ptr(), int(table_stride), T, nh, dk, rank, cache.shape[1], cache.shape[0], int(window or 0),
+        float(scale), _ptr(sink), int(row_groups), int(parts), _ptr(part_o), _ptr(part_ml), err.data_ptr(), _stream()),
+        "attn_latent_mma", 2 if parts > 1 else 1)
+
+
 def gate_sigmoid(out, heads, gate):
     """out[t, h, :] = heads[h, t, :] * sigmoid(gate[t, h, :]); ``gate`` may be a column range of a wider tensor."""
     nh, T, dv = heads.shape

@@ -460,3 +460,128 @@ def tidarax_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, h
     if int(err):
         raise RuntimeError("a kernel reported an error: " + kernels.describe_error(int(err)))
     return out
+
+
+def dufitar_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, head_dim: int = 128, intermediate: int = 12288,
+                    kv_rank: int = 512, rot_dim: int = 64, tokens: int = 2048, decode: Sequence[int] = (8, 4096),
+                    page_size: int = 16, hbm_gbs: float = 0.0, peak_tflops: float = 0.0, device="cuda:0") -> List[Dict]:
+    """One record per kernel of the Dufitar path: time, what it achieves and the share of its floor (bytes at the
+    measured copy rate, or tensor-core work at the measured matrix-product peak), each beside its like kernel of
+    the Qwen3 path.  The grouped-query layers' attention IS the Qwen3 path's tcgen05 kernel, so only the
+    attention over latent rows has a kernel of its own to compare."""
+    out: List[Dict] = []
+    err = torch.zeros(1, dtype=torch.int32, device=device)
+    bf = lambda *shape: torch.randn(*shape, device=device).bfloat16()
+    H, G, d, r, rd = heads, kv_heads, head_dim, kv_rank, rot_dim
+    dk = r + rd
+    sink = torch.randn(H, device=device)
+    from .parts import latent_attention as la
+
+    # attention over latent rows, a whole prompt: 2 heads (dk + rank) operations per (query, key) pair and head
+    ctx, table, stride, num_pages = _attention_context([(0, tokens)], page_size, device)
+    ctx.all_single = False
+    rows = bf(num_pages, page_size, dk)
+    q, o = bf(tokens, H, dk) * dk ** -0.5, torch.empty(tokens, H, r, dtype=torch.bfloat16, device=device)
+    pairs = tokens * (tokens + 1) / 2
+    us = _graph_time_us(lambda: la.latent_attend(o, q, rows, ctx, table, stride, page_size, None, 1.0, sink), 1, repeats=5)
+    tc = 2.0 * H * (dk + r) * pairs
+    floor_us = tc / (peak_tflops or 1590.0) / 1e6
+    out.append({"kernel": "latent attention, prompt (mma.sync)", "tokens": tokens, "us": round(us, 1),
+                "tensor_tflops": round(tc / us / 1e6, 1), "floor_us": round(floor_us, 1), "frac_of_floor": round(floor_us / us, 3)})
+    like = prefill_attention(((0, tokens),), heads=H, kv_heads=G, head_dim=d, page_size=page_size, peak_tflops=peak_tflops)[0]
+    out.append({"kernel": "like: Qwen3 prompt attention (tcgen05)", "tokens": tokens, "us": like["tcgen05_us"],
+                "tensor_tflops": like["tflops"], "frac_of_floor": like.get("frac_of_peak")})
+    del rows, q, o
+
+    # attention of single tokens over latent rows: one row of dk channels per key, whatever the number of heads
+    batch, context = decode
+    ctx, table, stride, num_pages = _attention_context([(context - 1, 1)] * batch, page_size, device)
+    ctx.all_single = True
+    layers = 4
+    caches = [bf(num_pages, page_size, dk) for _ in range(layers)]
+    q, o = bf(batch, H, dk) * dk ** -0.5, torch.empty(batch, H, r, dtype=torch.bfloat16, device=device)
+    nbytes = batch * context * dk * 2
+    us = _graph_time_us(lambda: [la.latent_attend(o, q, c, ctx, table, stride, page_size, None, 1.0, sink) for c in caches], layers)
+    floor_us = nbytes / (hbm_gbs or 6650.0) / 1e3
+    tc = 2.0 * H * (dk + r) * batch * context
+    out.append({"kernel": "latent attention, single tokens (mma.sync)", "batch": batch, "context": context, "us": round(us, 1),
+                "gbs": round(nbytes / us / 1e3, 1), "tensor_tflops": round(tc / us / 1e6, 1), "floor_us": round(floor_us, 1),
+                "frac_of_floor": round(floor_us / us, 3)})
+    like = decode_attention(((batch, context),), heads=H, kv_heads=G, head_dim=d, page_size=page_size, hbm_gbs=hbm_gbs)[0]
+    out.append({"kernel": "like: Qwen3 single-token attention (tcgen05)", "batch": batch, "context": context,
+                "us": like["tcgen05_us"], "gbs": like["gbs"], "frac_of_floor": like.get("frac_of_hbm")})
+    del caches, q, o
+
+    # the per-head maps into and out of the latent space (the library's batched product)
+    qp, w_uk = bf(tokens, H, d + rd), bf(H, d, r) * 0.02
+    q_lat = torch.empty(H, tokens, r, dtype=torch.bfloat16, device=device)
+    us = _loop_time_us(lambda: la.batched_product(q_lat, qp[:, :, :d].transpose(0, 1), w_uk.transpose(1, 2)))
+    fl = 2.0 * tokens * H * d * r
+    out.append({"kernel": "queries into the latent space (library batched product)", "tokens": tokens, "us": round(us, 1),
+                "tensor_tflops": round(fl / us / 1e6, 1), "frac_of_floor": round(fl / us / 1e6 / (peak_tflops or 1590.0), 3)})
+    o_lat, w_uv = bf(tokens, H, r), bf(H, d, r) * 0.02
+    o_heads = torch.empty(H, tokens, d, dtype=torch.bfloat16, device=device)
+    us = _loop_time_us(lambda: la.batched_product(o_heads, o_lat.transpose(0, 1), w_uv))
+    out.append({"kernel": "values out of the latent space (library batched product)", "tokens": tokens, "us": round(us, 1),
+                "tensor_tflops": round(fl / us / 1e6, 1), "frac_of_floor": round(fl / us / 1e6 / (peak_tflops or 1590.0), 3)})
+    del qp, q_lat, o_lat, o_heads
+
+    # the memory-bound kernels at a prompt portion's size; several sets of buffers, together larger than the L2
+    sets = 4
+
+    def record(name, nbytes, run, like=None):
+        us = _loop_time_us(lambda: [run(i) for i in range(sets)]) / sets
+        rec = {"kernel": name, "tokens": tokens, "bytes": nbytes, "us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1)}
+        if hbm_gbs:
+            rec["frac_of_floor"] = round(rec["gbs"] / hbm_gbs, 3)
+        if like:
+            rec["like"] = like
+        out.append(rec)
+
+    xs = [torch.randn(tokens, hidden, device=device) for _ in range(sets)]
+    bs = [torch.randn(tokens, hidden, device=device) for _ in range(sets)]
+    os_ = [torch.empty(tokens, hidden, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    alpha, w, b = torch.tensor(0.7, device=device), torch.randn(hidden, device=device), torch.randn(hidden, device=device)
+    record("Dynamic Tanh of the branch + scaled residual sum + Dynamic Tanh", tokens * hidden * (4 + 4 + 4 + 2),
+           lambda i: kernels.dyt_norm(os_[i], xs[i], alpha, w, b, err, branch=bs[i], branch_scale=0.7, branch_norm=(alpha, w, b),
+                                      sum_out=xs[i]), "residual sum + RMSNorm")
+    del xs, bs, os_
+    gus = [bf(tokens, 2 * intermediate) for _ in range(sets)]
+    acts = [torch.empty(tokens, intermediate, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    record("GELU (tanh form) gate", 3 * tokens * intermediate * 2, lambda i: kernels.swiglu(acts[i], gus[i], "gelu_tanh"), "SiLU gate")
+    del gus, acts
+    width = (H + 2 * G) * d
+    qkvs = [bf(tokens, width) for _ in range(sets)]
+    qs = [torch.empty(tokens, H, d, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    pages = (tokens + page_size - 1) // page_size
+    kcs = [torch.zeros(pages, G, page_size, d, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    vcs = [torch.zeros_like(k) for k in kcs]
+    inv = torch.rand(d // 4, device=device)
+    pos = torch.arange(tokens, dtype=torch.int32, device=device)
+    req = torch.zeros(tokens, dtype=torch.int32, device=device)
+    tab = torch.randperm(pages, device=device).to(torch.int32)
+    record("rotation of half a head + cache write", 2 * tokens * width * 2,
+           lambda i: kernels.qkv_prepare(qs[i], kcs[i], vcs[i], qkvs[i], None, None, inv, pos, req, tab, pages, H, G, d, d, d // 2,
+                                         True, 0, 1e-6, True, err, rot_magnitude=1.1), "q/k norm + rotation + cache write")
+    del qkvs, qs, kcs, vcs
+    nq = H * (d + rd)
+    projs = [bf(tokens, nq + H * d + dk) for _ in range(sets)]
+    qls = [bf(H, tokens, r) for _ in range(sets)]
+    qas = [torch.empty(tokens, H, dk, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    lcs = [torch.zeros(pages, page_size, dk, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    nw, inv2 = torch.randn(r, device=device), torch.rand(rd // 2, device=device)
+    record("latent norm + rotation + row write + query assembly", tokens * (H * rd + dk + H * r + H * dk + dk) * 2,
+           lambda i: kernels.latent_prepare(qas[i], lcs[i], projs[i], 0, nq + H * d, qls[i], nw, inv2, pos, req, tab, pages, H, d, rd,
+                                            r, rd, 1e-6, 1.0, err), "q/k norm + rotation + cache write")
+    ohs = [bf(H, tokens, d) for _ in range(sets)]
+    inns = [torch.empty(tokens, H * d, dtype=torch.bfloat16, device=device) for _ in range(sets)]
+    record("sigmoid gate on the heads' outputs", 3 * tokens * H * d * 2,
+           lambda i: kernels.gate_sigmoid(inns[i], ohs[i], projs[i][:, nq:nq + H * d]), "SiLU gate")
+    del projs, qls, qas, lcs, ohs, inns
+    for rec in prefill_elementwise(tokens, hidden=hidden, heads=H, kv_heads=G, head_dim=d, intermediate=intermediate,
+                                   page_size=page_size, hbm_gbs=hbm_gbs):
+        out.append({"kernel": "like: Qwen3 " + rec["kernel"], "tokens": tokens, "us": rec["us"], "gbs": rec["gbs"],
+                    "frac_of_floor": rec.get("frac_of_hbm")})
+    if int(err):
+        raise RuntimeError("a kernel reported an error: " + kernels.describe_error(int(err)))
+    return out

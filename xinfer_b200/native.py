@@ -120,6 +120,8 @@ def _declare_kernels(lib):
     _sig(lib, "xb_qkv_prepare", I, [I, P, P, P, P, P, P, P, P, P, P, I, I, I, I, I, I, I, I, I, I, I, F, I, F, P, P])
     _sig(lib, "xb_dyt_norm", I, [I, I, I, P, P, P, P, P, P, P, P, F, P, P, P, I, I, I, P, P])
     _sig(lib, "xb_latent_prepare", I, [I, P, P, P, L, I, I, P, L, L, P, P, P, P, P, I, I, I, I, I, I, I, I, I, F, F, P, P])
+    _sig(lib, "xb_attn_latent_mma_takes", I, [I, I])
+    _sig(lib, "xb_attn_latent_mma", I, [P, P, P, P, P, I, P, I, I, I, I, I, I, I, I, F, P, I, I, P, P, P, P])
     _sig(lib, "xb_gate_sigmoid", I, [I, P, P, L, L, P, L, I, I, I, P])
     _sig(lib, "xb_gemm_batched_plain", I, [I, P, P, P, I, I, I, I, L, L, L, L, L, L, L, P])
     _sig(lib, "xb_attn_talking_tile", I, [I, I, I, I])

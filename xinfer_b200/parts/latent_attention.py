@@ -37,6 +37,40 @@ def batched_product(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None
         kernels.gemm_batched_plain(out, a, w)
 
 
+# bfloat16: both products of the attention on tensor cores where the sizes allow; tests switch it off to compare
+USE_TENSOR_CORES = True
+# a step of single tokens deals every token's key tiles out to several blocks so that about one block per SM runs
+_DECODE_BLOCKS = 148
+_DECODE_MIN_TILES = 2
+
+
+def latent_attend(out, q, pages, ctx: StepContext, table, stride, page_size, window, scale, sink) -> None:
+    """Attention of ``q`` ``[T, heads, dk]`` over the cached rows ``pages`` ``[page, slot, dk]`` into ``out``
+    ``[T, heads, rank]``: on tensor cores in bfloat16 where the sizes fit, else one warp per (token, head)."""
+    T, H, dk = q.shape
+    rank = out.shape[-1]
+    if USE_TENSOR_CORES and q.dtype == torch.bfloat16 and kernels.attn_latent_mma_takes(dk, rank):
+        single = ctx.all_single or ctx.fixed_shapes
+        rg = 1 if (single and H <= 16) else 2
+        parts, part_o, part_ml = 1, None, None
+        if single:
+            # key ranges: a replayed step must not look at its actual lengths
+            bound = stride * page_size if ctx.fixed_shapes else ctx.max_context
+            if window:
+                bound = min(bound, window + 63)
+            tiles = (max(bound, 1) + 63) // 64
+            blocks = max(T, 1) * ((H + 16 * rg - 1) // (16 * rg))
+            parts = max(1, min(_DECODE_BLOCKS // blocks, tiles // _DECODE_MIN_TILES, 64))
+            if parts > 1:
+                part_o = ctx.workspace.get("latent.part_o", (T * H * parts * rank,), torch.float32)
+                part_ml = ctx.workspace.get("latent.part_ml", (T * H * parts * 2,), torch.float32)
+        kernels.attn_latent_mma(out, q, pages, ctx.q_start, ctx.start_pos, ctx.num_entries, table, stride, window, scale,
+                                sink, ctx.err, row_groups=rg, parts=parts, part_o=part_o, part_ml=part_ml)
+        return
+    kernels.attention_plain(out, q, pages.view(pages.shape[0], 1, pages.shape[1], dk), None, ctx.positions,
+                            ctx.req_of_token, table, stride, window, scale, ctx.err, sink=sink, value_dim=rank)
+
+
 class LatentAttention(Mixer):
     kind = "latent_attention"
     graph_safe = True
@@ -117,8 +151,7 @@ class LatentAttention(Mixer):
                                rope.rotary_dim, s.norm_eps, rope.magnitude, ctx.err)
         # one key/value head over the cached rows: keys are the whole row, values its first kv_rank channels
         o_lat = ws.get("latent.o_lat", (T, H, r), self.dtype)
-        kernels.attention_plain(o_lat, q_abs, pages.view(pages.shape[0], 1, pages.shape[1], r + rd), None, ctx.positions,
-                                ctx.req_of_token, table, stride, s.window, s.scale, ctx.err, sink=self.sink, value_dim=r)
+        latent_attend(o_lat, q_abs, pages, ctx, table, stride, cache.page_size, s.window, s.scale, self.sink)
         # back out of the latent space, head by head: o[h] = o_lat[h] . W_uv,h^T
         o_heads = ws.get("latent.o_heads", (H, T, dv), self.dtype)
         batched_product(o_heads, o_lat.transpose(0, 1), self.w_uv)

@@ -31,6 +31,8 @@ _DECODE_BLOCKS = 148
 _DECODE_MIN_KEYS = 128
 # bfloat16: both products on tensor cores where the sizes allow; tests switch it off to compare the two forms
 USE_TENSOR_CORES = True
+# without a mix and a sink the attention is the ordinary one: use the kernels of the engine's attention backend
+USE_ATTENTION_BACKEND = True
 
 
 class TalkingAttention(Mixer):
@@ -80,6 +82,20 @@ class TalkingAttention(Mixer):
         return PagedCacheNeed((("k", CacheTensor((s.num_kv_heads, s.head_dim), None, 1)),
                                ("v", CacheTensor((s.num_kv_heads, s.value_dim), None, 1))), s.window)
 
+    def _plain_softmax(self) -> bool:
+        """No mix across heads, no sink, key and value heads of one size in bfloat16: the attention itself is the
+        ordinary grouped-query one, and the engine's tcgen05 kernels (work lists, decode plans) take it."""
+        s = self.spec
+        return (USE_ATTENTION_BACKEND and not s.talking_heads and not s.sink and s.value_dim == s.head_dim
+                and self.dtype == torch.bfloat16 and kernels.attn_tiled_supported(self.dtype, s.head_dim))
+
+    def prepare_step(self, ctx: StepContext, cache: LayerCache) -> None:
+        if self._plain_softmax():
+            from . import attention_backend
+            s = self.spec
+            attention_backend.prepare_step(ctx, self.dtype, s.num_heads, s.num_kv_heads, s.head_dim, cache.page_size,
+                                           s.window, ctx.strides[cache.group])
+
     # ---- the two halves ---------------------------------------------------------------------------
     def inner_width(self) -> int:
         return self.spec.num_heads * self.spec.value_dim
@@ -103,6 +119,10 @@ class TalkingAttention(Mixer):
                             table, stride, nh, nkv, d, dv, rope.rotary_dim if rope is not None else 0,
                             rope is not None and rope.layout == "interleaved", norm_mode, s.qk_norm_eps, writes_cache,
                             ctx.err, rot_magnitude=rope.magnitude if rope is not None else 1.0)
+        if self._plain_softmax() and out_scale == 1.0 and out.is_contiguous():
+            from . import attention_backend
+            attention_backend.attend(out.view(T, nh, dv), q, cache, ctx, table, stride, s.window, s.scale)
+            return
         # queries per block: the longest portion decides (a step of single tokens takes one query per block
         # and cuts the keys instead); a replayed step must not look at its actual lengths
         single = ctx.all_single or ctx.fixed_shapes
