@@ -177,8 +177,11 @@ def test_batched_product_takes_views_in_both_weight_orders(dtype):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("given", [True, False])
 @pytest.mark.parametrize("H,d,rd,rank,shares", [(3, 8, 4, 20, False), (5, 16, 8, 24, True), (2, 6, 2, 14, False)])
-def test_latent_prepare_norms_rotates_and_writes_rows(dtype, H, d, rd, rank, shares):
+def test_latent_prepare_norms_rotates_and_writes_rows(dtype, H, d, rd, rank, shares, given):
+    """``given``: the queries' latent parts come as a tensor of their own and are copied; otherwise they lie in the
+    query rows already (the product that forms them writes them there) and must stay as they are."""
     k = _k()
     ps, T, eps = 8, 14, 1e-5
     rot = dict(dims=rd, base=300.0)
@@ -192,8 +195,11 @@ def test_latent_prepare_norms_rotates_and_writes_rows(dtype, H, d, rd, rank, sha
     table = torch.arange(2 * 16, dtype=torch.int32).view(2, 16).flip(0).contiguous()
     cache = torch.zeros(32, ps, rank + rd, dtype=dtype, device=DEV)
     q_abs = torch.zeros(T, H, rank + rd, dtype=dtype, device=DEV)
+    if not given:
+        q_abs[:, :, :rank] = q_lat.transpose(0, 1).to(DEV)
     err = _err()
-    k.latent_prepare(q_abs, cache, proj.to(DEV), 0, -1 if shares else nq + extra, q_lat.to(DEV), None if shares else norm_w.to(DEV),
+    k.latent_prepare(q_abs, cache, proj.to(DEV), 0, -1 if shares else nq + extra, q_lat.to(DEV) if given else None,
+                     None if shares else norm_w.to(DEV),
                      freq.to(DEV), _i32(positions.tolist()), _i32(req.tolist()), table.to(DEV), 16, H, d, rd, rank, rd, eps, 1.0, err)
     assert int(err.item()) == 0
     x = proj.double()
@@ -215,15 +221,22 @@ def test_latent_prepare_norms_rotates_and_writes_rows(dtype, H, d, rd, rank, sha
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_gate_multiplies_heads_by_a_sigmoid(dtype):
+@pytest.mark.parametrize("H,T,dv,lead", [(3, 11, 10, 7), (4, 70, 16, 8), (2, 5, 24, 16)])
+def test_gate_multiplies_heads_by_a_sigmoid(dtype, H, T, dv, lead):
+    """Heads laid out head by head into a fresh tensor, and in place on heads that lie token by token (the second and
+    third sizes take 16-byte accesses in bfloat16)."""
     k = _k()
-    H, T, dv = 3, 11, 10
     heads = _rand(H, T, dv, seed=1).to(dtype)
-    wide = _rand(T, 7 + H * dv + 2, seed=2, scale=3.0).to(dtype).to(DEV)
+    wide = _rand(T, lead + H * dv + 8, seed=2, scale=3.0).to(dtype).to(DEV)
+    gate = wide[:, lead:lead + H * dv]
+    want = heads.double().transpose(0, 1).reshape(T, H * dv) * torch.sigmoid(gate.double().cpu())
+    tol = (1e-6 if dtype == torch.float32 else 2e-2) * (1 + want.abs().max())
     out = torch.zeros(T, H * dv, dtype=dtype, device=DEV)
-    k.gate_sigmoid(out, heads.to(DEV), wide[:, 7:7 + H * dv])
-    want = heads.double().transpose(0, 1).reshape(T, H * dv) * torch.sigmoid(wide[:, 7:7 + H * dv].double().cpu())
-    assert (out.double().cpu() - want).abs().max() <= (1e-6 if dtype == torch.float32 else 2e-2) * (1 + want.abs().max())
+    k.gate_sigmoid(out, heads.to(DEV), gate)
+    assert (out.double().cpu() - want).abs().max() <= tol
+    inner = heads.transpose(0, 1).reshape(T, H * dv).contiguous().to(DEV)
+    k.gate_sigmoid(inner, inner.view(T, H, dv).transpose(0, 1), gate)
+    assert (inner.double().cpu() - want).abs().max() <= tol
 
 
 # ---------------------------------------------------------------------------------------------
@@ -598,3 +611,23 @@ def test_long_greedy_decoding_in_bfloat16_follows_the_plain_logits(graphs, tmp_p
         for i, tok in enumerate(o.decode_output):
             row = ref[len(p) + i - 1]
             assert row[tok] >= row.max() - slack, (i, tok)
+
+
+def test_command_line_writes_a_random_folder_and_generates_from_it(tmp_path, capsys):
+    """The command line end to end: a folder from a configuration and a seed, then generation from given ids (equal
+    to the plain continuation in float32) and from a seeded prompt of a given length."""
+    import json
+    from xinfer_b200.cli import main
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(TINY_D["D4"][0]))
+    folder = str(tmp_path / "model")
+    assert main(["--random", str(config), "--seed", "4", "--m", folder, "--store-dtype", "f32"]) == 0
+    cfg, w = plain.load_folder(folder)
+    capsys.readouterr()
+    assert main(["--m", folder, "--dtype", "f32", "--prompts", "5,6,7|9,10", "--max-tokens", "4", "--ignore-eos",
+                 "--disable-cuda-graph", "--num-blocks", "16"]) == 0
+    out = capsys.readouterr().out
+    assert ",".join(str(t) for t in plain.generate(cfg, w, [5, 6, 7], 4)) in out and "Decoded tokens: 8" in out
+    assert main(["--m", folder, "--prompt-len", "21", "--batch", "3", "--max-tokens", "5", "--ignore-eos", "--num-blocks", "16",
+                 "--seed", "1"]) == 0
+    assert "Decoded tokens: 15" in capsys.readouterr().out

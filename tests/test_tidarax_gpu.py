@@ -572,7 +572,7 @@ def test_layers_one_by_one_in_float32(tmp_path):
         out = orig(self, stream, ctx, cache, state, writes_cache)
         x = out.x.double().clone()
         for b in out.pending:
-            x += b.double()
+            x += b.scale * b.plain(ctx).double()
         rec.append(x.cpu())
         return out
 

@@ -20,7 +20,7 @@ from typing import List, Optional
 
 
 def build_parser() -> argparse.ArgumentParser:
-    ap = argparse.ArgumentParser(prog="xinfer_b200", description="Qwen3 inference on one B200")
+    ap = argparse.ArgumentParser(prog="xinfer_b200", description="decoder inference on one B200 (Qwen3, Tidarax, Dufitar)")
     ap.add_argument("--m", dest="model_id", help="model folder (config.json and model.safetensors)")
     ap.add_argument("--w", dest="weight_path", help="same as --m (the reference's older spelling)")
     ap.add_argument("--dtype", default="bf16", help="bf16 (default) or f32")
@@ -96,9 +96,9 @@ def main(argv: Optional[List[str]] = None) -> int:
     if args.prompts:
         prompts = _parse_prompts(args.prompts)
     else:
-        _, cfg = load_config(folder)
+        entry, cfg = load_config(folder)
         rng = np.random.default_rng(args.seed or 0)
-        prompts = [rng.integers(0, cfg.vocab_size, size=args.prompt_len or 16).tolist()]
+        prompts = [rng.integers(0, entry.plan_of(cfg).vocab_size, size=args.prompt_len or 16).tolist()]
     if args.batch:
         prompts = [prompts[0]] * args.batch
     # sampling flags make the engine's default options, as in the reference (src/main.rs:117-135); they come

@@ -15,7 +15,7 @@
 // proj[t] holds the step's packed projection of token t: the queries at q_off (heads x (d + rd), a head as
 // [d plain | rd to rotate]) and, at kv_off, [kv_rank latent | rd key part] (kv_off < 0: this layer reads the
 // rows another layer wrote).  q_lat[t, h] (strides given) is the head's query already carried into the latent
-// space.  The first `rot` channels of a rotated part turn by position * inv_freq[pair] (pairs 2i, 2i+1), cos
+// space; absent: the latent part of q_abs has been written already (by the product that formed it) and stays.  The first `rot` channels of a rotated part turn by position * inv_freq[pair] (pairs 2i, 2i+1), cos
 // and sin times rot_mag; the others pass.
 template <typename T>
 __global__ void latent_prepare_kernel(T* __restrict__ q_abs, T* __restrict__ cache, const T* __restrict__ proj,
@@ -43,21 +43,21 @@ __global__ void latent_prepare_kernel(T* __restrict__ q_abs, T* __restrict__ cac
     const T* row = proj + (size_t)t * row_len;
     const int dk = rank + rd;
     // queries: [latent part | rotated part]
-    for (int i = threadIdx.x; i < nh * dk; i += blockDim.x) {
-        const int h = i / dk, c = i % dk;
-        float v;
-        if (c < rank) {
-            v = to_f32<T>(q_lat[(size_t)t * ql_ts + (size_t)h * ql_hs + c]);
-        } else {
-            const int e = c - rank;
-            const T* qr = row + q_off + (size_t)h * (d + rd) + d;
-            v = to_f32<T>(qr[e]);
-            if (e < rot) {
-                const float o = to_f32<T>(qr[e ^ 1]);
-                v = (e & 1) ? fmaf(v, cs[e >> 1], o * sn[e >> 1]) : fmaf(v, cs[e >> 1], -o * sn[e >> 1]);
-            }
+    if (q_lat != nullptr) {
+        for (int i = threadIdx.x; i < nh * rank; i += blockDim.x) {
+            const int h = i / rank, c = i % rank;
+            q_abs[((size_t)t * nh + h) * dk + c] = q_lat[(size_t)t * ql_ts + (size_t)h * ql_hs + c];
         }
-        q_abs[(size_t)t * nh * dk + i] = from_f32<T>(v);
+    }
+    for (int i = threadIdx.x; i < nh * rd; i += blockDim.x) {
+        const int h = i / rd, e = i % rd;
+        const T* qr = row + q_off + (size_t)h * (d + rd) + d;
+        float v = to_f32<T>(qr[e]);
+        if (e < rot) {
+            const float o = to_f32<T>(qr[e ^ 1]);
+            v = (e & 1) ? fmaf(v, cs[e >> 1], o * sn[e >> 1]) : fmaf(v, cs[e >> 1], -o * sn[e >> 1]);
+        }
+        q_abs[((size_t)t * nh + h) * dk + rank + e] = from_f32<T>(v);
     }
     if (kv_off < 0 || b < 0) return;
     const int page = block_table[(size_t)b * table_stride + pos / page_size];
@@ -98,7 +98,7 @@ XB_EXPORT int xb_latent_prepare(int dtype, void* q_abs, void* cache, const void*
     if (rot % 2 || rot > rd) return (int)cudaErrorInvalidValue;
     const size_t smem = (size_t)rot * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
-    const int work = nh * (rank + rd);
+    const int work = q_lat != nullptr ? nh * (rank + rd) : (nh * rd > rank + rd ? nh * rd : rank + rd);
     const int threads = work >= 4096 ? 512 : (work >= 1024 ? 256 : 128);
 #define XB_GO(T)                                                                                                        \
     latent_prepare_kernel<T><<<tokens, threads, smem, stream>>>((T*)q_abs, (T*)cache, (const T*)proj, row_len, q_off,  \
@@ -110,9 +110,10 @@ XB_EXPORT int xb_latent_prepare(int dtype, void* q_abs, void* cache, const void*
     return xb_launch_status();
 }
 
-// out[t, h * dv + v] = heads[t * h_ts + h * h_hs + v] * sigmoid(gate[t * g_ts + h * dv + v])   (float32 arithmetic)
+// out[t, h * dv + v] = heads[t * h_ts + h * h_hs + v] * sigmoid(gate[t * g_ts + h * dv + v])   (float32 arithmetic);
+// `heads` may be `out` itself laid out the same way (in place)
 template <typename T>
-__global__ void gate_sigmoid_kernel(T* __restrict__ out, const T* __restrict__ heads, long long h_ts, long long h_hs,
+__global__ void gate_sigmoid_kernel(T* out, const T* heads, long long h_ts, long long h_hs,
                                     const T* __restrict__ gate, long long g_ts, int nh, int dv, size_t n) {
     const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n) return;
@@ -124,10 +125,40 @@ __global__ void gate_sigmoid_kernel(T* __restrict__ out, const T* __restrict__ h
     out[i] = from_f32<T>(o / (1.f + expf(-g)));
 }
 
+// eight bfloat16 elements per thread with 16-byte accesses (dv and every stride a multiple of 8, pointers aligned)
+__global__ void gate_sigmoid_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* heads, long long h_ts,
+                                           long long h_hs, const __nv_bfloat16* __restrict__ gate, long long g_ts, int nh,
+                                           int dv, size_t nvec) {
+    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= nvec) return;
+    const size_t w = (size_t)nh * dv / 8;
+    const size_t t = i / w, c = (i % w) * 8;
+    const int h = (int)(c / dv), v = (int)(c % dv);
+    const uint4 pg = *reinterpret_cast<const uint4*>(gate + t * g_ts + c);
+    const uint4 po = *reinterpret_cast<const uint4*>(heads + t * h_ts + (size_t)h * h_hs + v);
+    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&pg);
+    const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&po);
+    uint4 res;
+    __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+        const float2 g = __bfloat1622float2(g2[k]), o = __bfloat1622float2(o2[k]);
+        r2[k] = __floats2bfloat162_rn(o.x / (1.f + expf(-g.x)), o.y / (1.f + expf(-g.y)));
+    }
+    *reinterpret_cast<uint4*>(out + t * w * 8 + c) = res;
+}
+
 XB_EXPORT int xb_gate_sigmoid(int dtype, void* out, const void* heads, long long h_ts, long long h_hs, const void* gate,
                               long long g_ts, int tokens, int nh, int dv, cudaStream_t stream) {
     const size_t n = (size_t)tokens * nh * dv;
     if (n == 0) return 0;
+    if (dtype == XB_BF16 && dv % 8 == 0 && h_ts % 8 == 0 && h_hs % 8 == 0 && g_ts % 8 == 0 &&
+        !(((uintptr_t)out | (uintptr_t)heads | (uintptr_t)gate) & 15)) {
+        const size_t nvec = n / 8;
+        gate_sigmoid_bf16x8_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, stream>>>(
+            (__nv_bfloat16*)out, (const __nv_bfloat16*)heads, h_ts, h_hs, (const __nv_bfloat16*)gate, g_ts, nh, dv, nvec);
+        return xb_launch_status();
+    }
     const unsigned blocks = (unsigned)((n + 255) / 256);
     if (dtype == XB_F32)
         gate_sigmoid_kernel<float><<<blocks, 256, 0, stream>>>((float*)out, (const float*)heads, h_ts, h_hs, (const float*)gate, g_ts, nh, dv, n);

@@ -7,9 +7,10 @@
 //
 //   a. the tile's cached rows to shared memory by 16-byte asynchronous copies, one tile ahead (two buffers);
 //      rows outside the request are zero-filled;
-//   b. S = Q K^T: the four warps of a row group take 16 keys each (k runs over all dk channels);
-//      the scores go to shared memory as float32;
-//   c. every warp reads its row group's scores in the layout of an A operand, applies scale, causal mask and
+//   b. S = Q K^T: the four warps of a row group share the dk channels (16-channel steps w, w + 4, ...) and each
+//      forms a partial score of all 64 keys - eight independent accumulator tiles per warp; the four partial
+//      scores go to shared memory as float32;
+//   c. every warp sums its row group's partial scores in the layout of an A operand, applies scale, causal mask and
 //      window, and keeps the running maximum and sum of its rows (the four warps of a row group compute the
 //      same numbers); a head's sink enters as the start of maximum and sum;
 //   d. O <- O * correction + P V: the four warps of a row group take the value columns in turn (8-column
@@ -44,7 +45,7 @@ struct LatentMmaArgs {
 
 __host__ __device__ inline size_t latent_mma_smem(int dk, int rg) {
     const size_t ld = dk + 8;
-    return (size_t)(16 * rg + 2 * LM_BK) * ld * 2 + (size_t)16 * rg * LM_LDS * 4;
+    return (size_t)(16 * rg + 2 * LM_BK) * ld * 2 + (size_t)4 * 16 * rg * LM_LDS * 4;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
@@ -101,24 +102,25 @@ __global__ void __launch_bounds__(256) attn_latent_mma_kernel(__nv_bfloat16* __r
         *reinterpret_cast<uint4*>(Qs + (size_t)r * ld + c * 8) = v;
     }
 
+    const int nwarps = blockDim.x >> 5;
+    // a warp per cached row (one page lookup), its lanes over the row's 16-byte pieces
     auto fetch = [&](int t, int buf) {
         const int k0 = k_begin + t * LM_BK;
         __nv_bfloat16* dst = Ks + (size_t)buf * LM_BK * ld;
-        for (int e = tid; e < LM_BK * chunks; e += blockDim.x) {
-            const int r = e / chunks, c = e - r * chunks;
+        for (int r = warp; r < LM_BK; r += nwarps) {
             const int j = k0 + r;
-            const __nv_bfloat16* src = cache;
-            int bytes = 0;
+            const __nv_bfloat16* src = nullptr;
             if (j <= p_hi) {
                 const int page = table[j / a.page_size];
                 if (page < 0 || page >= a.num_pages) {
-                    atomicOr(a.err, XB_ERR_BAD_PAGE);
+                    if (lane == 0) atomicOr(a.err, XB_ERR_BAD_PAGE);
                 } else {
-                    src = cache + ((size_t)page * a.page_size + (j % a.page_size)) * dk + c * 8;
-                    bytes = 16;
+                    src = cache + ((size_t)page * a.page_size + (j % a.page_size)) * dk;
                 }
             }
-            cp_async16(smem_addr(dst + (size_t)r * ld + c * 8), src, bytes);
+            const uint32_t d0 = smem_addr(dst + (size_t)r * ld);
+            for (int c = lane; c < chunks; c += 32)
+                cp_async16(d0 + c * 16, src ? src + c * 8 : cache, src ? 16 : 0);
         }
         cp_async_commit();
     };
@@ -157,24 +159,28 @@ __global__ void __launch_bounds__(256) attn_latent_mma_kernel(__nv_bfloat16* __r
         const __nv_bfloat16* Kt = Ks + (size_t)buf * LM_BK * ld;
         const int k0 = k_begin + t * LM_BK;
 
-        // b. scores of this warp's 16 keys
-        float s[2][4] = {{0.f, 0.f, 0.f, 0.f}, {0.f, 0.f, 0.f, 0.f}};
+        // b. this warp's share of the channels, all 64 keys: a partial score tile
         {
+            float s[8][4];
+#pragma unroll
+            for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
             const int mi = lane >> 3, rr = lane & 7;
             const uint32_t qa = smem_addr(Qs + (size_t)(rgi * 16 + (mi & 1) * 8 + rr) * ld + (mi >> 1) * 8);
-            const uint32_t ka = smem_addr(Kt + (size_t)(cw * 16 + (mi >> 1) * 8 + rr) * ld + (mi & 1) * 8);
-            for (int ks = 0; ks < dk / 16; ++ks) {
-                uint32_t af[4], bf[4];
+            const uint32_t ka = smem_addr(Kt + (size_t)((mi >> 1) * 8 + rr) * ld + (mi & 1) * 8);
+            for (int ks = cw; ks < dk / 16; ks += 4) {
+                uint32_t af[4];
                 ldmatrix_x4(af, qa + ks * 32);
-                ldmatrix_x4(bf, ka + ks * 32);
-                mma_bf16(s[0], af, bf[0], bf[1]);
-                mma_bf16(s[1], af, bf[2], bf[3]);
-            }
-        }
-        {
-            float* srow = Ss + (size_t)(rgi * 16 + (lane >> 2)) * LM_LDS + cw * 16 + 2 * quad;
 #pragma unroll
-            for (int n = 0; n < 2; ++n) {
+                for (int kb = 0; kb < 4; ++kb) {
+                    uint32_t bf[4];
+                    ldmatrix_x4(bf, ka + (uint32_t)(kb * 16 * ld * 2) + ks * 32);
+                    mma_bf16(s[2 * kb], af, bf[0], bf[1]);
+                    mma_bf16(s[2 * kb + 1], af, bf[2], bf[3]);
+                }
+            }
+            float* srow = Ss + ((size_t)cw * R + rgi * 16 + (lane >> 2)) * LM_LDS + 2 * quad;
+#pragma unroll
+            for (int n = 0; n < 8; ++n) {
                 *reinterpret_cast<float2*>(srow + n * 8) = make_float2(s[n][0], s[n][1]);
                 *reinterpret_cast<float2*>(srow + 8 * LM_LDS + n * 8) = make_float2(s[n][2], s[n][3]);
             }
@@ -193,7 +199,13 @@ __global__ void __launch_bounds__(256) attn_latent_mma_kernel(__nv_bfloat16* __r
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
                     const int col = kk * 16 + hf * 8 + 2 * quad;
-                    const float2 v = *reinterpret_cast<const float2*>(srow + col);
+                    float2 v = *reinterpret_cast<const float2*>(srow + col);
+#pragma unroll
+                    for (int c = 1; c < 4; ++c) {
+                        const float2 u = *reinterpret_cast<const float2*>(srow + (size_t)c * R * LM_LDS + col);
+                        v.x += u.x;
+                        v.y += u.y;
+                    }
                     const int j = k0 + col;
                     const bool see0 = j <= rpos[i] && (a.window <= 0 || j > rpos[i] - a.window);
                     const bool see1 = j + 1 <= rpos[i] && (a.window <= 0 || j + 1 > rpos[i] - a.window);

@@ -878,14 +878,16 @@ def expert_combine(out, y, inv, top: int):
 def latent_prepare(q_abs, cache, proj, q_off, kv_off, q_lat, norm_w, inv_freq, positions, req_of_token, block_table,
                    table_stride, nh, d, rd, rank, rot, eps, rot_magnitude, err):
     """Per token of the packed projection ``proj``: the query of every head as ``q_abs[t, h] = [q_lat[h, t] | rotated
-    rd channels]`` (``q_lat`` ``[heads, T, rank]``: the plain query part carried into the latent space), and, with
+    rd channels]`` (``q_lat`` ``[heads, T, rank]``: the plain query part carried into the latent space; None: the
+    product that formed it has written it into ``q_abs`` already), and, with
     ``kv_off`` >= 0, the cached row ``[RMS-normed rank channels * norm_w | rotated rd channels]`` into its page
     (``cache`` ``[page, slot, rank + rd]``).  Rotation: pairs (2i, 2i + 1) of the first ``rot`` channels by
     ``position * inv_freq[i]``, cos and sin times ``rot_magnitude``."""
     T = proj.shape[0]
     _need(proj, "proj", None, (T, None))
     _need(q_abs, "q_abs", proj.dtype, (T, nh, rank + rd))
-    _need(q_lat, "q_lat", proj.dtype, (nh, T, rank))
+    if q_lat is not None:
+        _need(q_lat, "q_lat", proj.dtype, (nh, T, rank))
     _need(cache, "cache", proj.dtype, (None, None, rank + rd))
     _need(inv_freq, "inv_freq", torch.float32, (rot // 2,))
     if kv_off >= 0:
@@ -896,7 +898,7 @@ def latent_prepare(q_abs, cache, proj, q_off, kv_off, q_lat, norm_w, inv_freq, p
         raise KernelError("the queries lie outside the projection's rows")
     _ok(kernels_lib().xb_latent_prepare(
         dtype_code(proj.dtype), q_abs.data_ptr(), cache.data_ptr(), proj.data_ptr(), proj.shape[1], int(q_off), int(kv_off),
-        q_lat.data_ptr(), rank, T * rank, _ptr(norm_w), inv_freq.data_ptr(), positions.data_ptr(), req_of_token.data_ptr(),
+        _ptr(q_lat), rank, T * rank, _ptr(norm_w), inv_freq.data_ptr(), positions.data_ptr(), req_of_token.data_ptr(),
         block_table.data_ptr(), int(table_stride), T, nh, d, rd, rank, int(rot), cache.shape[1], cache.shape[0], float(eps),
         float(rot_magnitude), err.data_ptr(), _stream()), "latent_prepare")
 
@@ -934,14 +936,17 @@ def attn_latent_mma(out, q, cache, q_start, start_pos, num_entries, block_table,
 
 
 def gate_sigmoid(out, heads, gate):
-    """out[t, h, :] = heads[h, t, :] * sigmoid(gate[t, h, :]); ``gate`` may be a column range of a wider tensor."""
+    """out[t, h, :] = heads[h, t, :] * sigmoid(gate[t, h, :]).  ``heads`` ``[heads, T, dv]`` may be any view with a
+    unit last stride - also ``out`` itself seen head by head (in place); ``gate`` may be a column range of a wider
+    tensor."""
     nh, T, dv = heads.shape
-    _need(heads, "heads", None, (nh, T, dv))
+    if not heads.is_cuda or heads.stride(2) != 1:
+        raise KernelError("heads must be a CUDA view [heads, T, dv] with a unit last stride")
     _need(out, "out", heads.dtype, (T, nh * dv))
     if (gate.dtype != heads.dtype or tuple(gate.shape) != (T, nh * dv) or gate.stride(1) != 1 or not gate.is_cuda):
         raise KernelError("gate must be a [T, heads * dv] view with unit column stride in the heads' type")
-    _ok(kernels_lib().xb_gate_sigmoid(dtype_code(heads.dtype), out.data_ptr(), heads.data_ptr(), dv, T * dv, gate.data_ptr(),
-                                      gate.stride(0), T, nh, dv, _stream()), "gate_sigmoid")
+    _ok(kernels_lib().xb_gate_sigmoid(dtype_code(heads.dtype), out.data_ptr(), heads.data_ptr(), heads.stride(1), heads.stride(0),
+                                      gate.data_ptr(), gate.stride(0), T, nh, dv, _stream()), "gate_sigmoid")
 
 
 def gemm_batched_plain(out, a, w):

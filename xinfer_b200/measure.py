@@ -514,13 +514,13 @@ def dufitar_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, h
 
     # the per-head maps into and out of the latent space (the library's batched product)
     qp, w_uk = bf(tokens, H, d + rd), bf(H, d, r) * 0.02
-    q_lat = torch.empty(H, tokens, r, dtype=torch.bfloat16, device=device)
+    q_lat = torch.empty(tokens, H, dk, dtype=torch.bfloat16, device=device)[:, :, :r].transpose(0, 1)
     us = _loop_time_us(lambda: la.batched_product(q_lat, qp[:, :, :d].transpose(0, 1), w_uk.transpose(1, 2)))
     fl = 2.0 * tokens * H * d * r
     out.append({"kernel": "queries into the latent space (library batched product)", "tokens": tokens, "us": round(us, 1),
                 "tensor_tflops": round(fl / us / 1e6, 1), "frac_of_floor": round(fl / us / 1e6 / (peak_tflops or 1590.0), 3)})
     o_lat, w_uv = bf(tokens, H, r), bf(H, d, r) * 0.02
-    o_heads = torch.empty(H, tokens, d, dtype=torch.bfloat16, device=device)
+    o_heads = torch.empty(tokens, H, d, dtype=torch.bfloat16, device=device).transpose(0, 1)
     us = _loop_time_us(lambda: la.batched_product(o_heads, o_lat.transpose(0, 1), w_uv))
     out.append({"kernel": "values out of the latent space (library batched product)", "tokens": tokens, "us": round(us, 1),
                 "tensor_tflops": round(fl / us / 1e6, 1), "frac_of_floor": round(fl / us / 1e6 / (peak_tflops or 1590.0), 3)})
@@ -566,18 +566,17 @@ def dufitar_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, h
     del qkvs, qs, kcs, vcs
     nq = H * (d + rd)
     projs = [bf(tokens, nq + H * d + dk) for _ in range(sets)]
-    qls = [bf(H, tokens, r) for _ in range(sets)]
     qas = [torch.empty(tokens, H, dk, dtype=torch.bfloat16, device=device) for _ in range(sets)]
     lcs = [torch.zeros(pages, page_size, dk, dtype=torch.bfloat16, device=device) for _ in range(sets)]
     nw, inv2 = torch.randn(r, device=device), torch.rand(rd // 2, device=device)
-    record("latent norm + rotation + row write + query assembly", tokens * (H * rd + dk + H * r + H * dk + dk) * 2,
-           lambda i: kernels.latent_prepare(qas[i], lcs[i], projs[i], 0, nq + H * d, qls[i], nw, inv2, pos, req, tab, pages, H, d, rd,
+    record("latent norm + rotation of the shared key part and of the queries' rotated parts + row write",
+           tokens * 2 * (H * rd + dk) * 2,
+           lambda i: kernels.latent_prepare(qas[i], lcs[i], projs[i], 0, nq + H * d, None, nw, inv2, pos, req, tab, pages, H, d, rd,
                                             r, rd, 1e-6, 1.0, err), "q/k norm + rotation + cache write")
-    ohs = [bf(H, tokens, d) for _ in range(sets)]
-    inns = [torch.empty(tokens, H * d, dtype=torch.bfloat16, device=device) for _ in range(sets)]
-    record("sigmoid gate on the heads' outputs", 3 * tokens * H * d * 2,
-           lambda i: kernels.gate_sigmoid(inns[i], ohs[i], projs[i][:, nq:nq + H * d]), "SiLU gate")
-    del projs, qls, qas, lcs, ohs, inns
+    inns = [bf(tokens, H * d) for _ in range(sets)]
+    record("sigmoid gate on the heads' outputs (in place)", 3 * tokens * H * d * 2,
+           lambda i: kernels.gate_sigmoid(inns[i], inns[i].view(tokens, H, d).transpose(0, 1), projs[i][:, nq:nq + H * d]), "SiLU gate")
+    del projs, qas, lcs, inns
     for rec in prefill_elementwise(tokens, hidden=hidden, heads=H, kv_heads=G, head_dim=d, intermediate=intermediate,
                                    page_size=page_size, hbm_gbs=hbm_gbs):
         out.append({"kernel": "like: Qwen3 " + rec["kernel"], "tokens": tokens, "us": rec["us"], "gbs": rec["gbs"],

@@ -31,7 +31,7 @@ from .linear import linear
 def batched_product(out: torch.Tensor, a: torch.Tensor, w: torch.Tensor) -> None:
     """out[b] = a[b] . w[b]^T for every b (``a`` [B, M, K], ``w`` [B, N, K], views allowed): the library's batched
     product in bfloat16, the engine's FMA kernel in float32 (true 32-bit)."""
-    if a.dtype == torch.bfloat16 and out.is_contiguous():
+    if a.dtype == torch.bfloat16:
         torch.bmm(a, w.transpose(1, 2), out=out)
     else:
         kernels.gemm_batched_plain(out, a, w)
@@ -138,28 +138,27 @@ class LatentAttention(Mixer):
         width = self.w_in.shape[0]
         proj = ws.get("latent.proj", (T, width), self.dtype)
         linear(proj, x, self.w_in, ctx.err)
-        # every head's plain query part carried into the latent space: q_lat[h] = q_plain[h] . W_uk,h
+        # every head's plain query part carried into the latent space, q_lat[h] = q_plain[h] . W_uk,h, written
+        # straight into the front of the head's query row
         q_plain = proj[:, :nq].view(T, H, d + rd)[:, :, :d].transpose(0, 1)          # [H, T, d] view
-        q_lat = ws.get("latent.q_lat", (H, T, r), self.dtype)
-        batched_product(q_lat, q_plain, self.w_uk.transpose(1, 2))
+        q_abs = ws.get("latent.q", (T, H, r + rd), self.dtype)
+        batched_product(q_abs[:, :, :r].transpose(0, 1), q_plain, self.w_uk.transpose(1, 2))
         pages = cache["latent"]
         table, stride = ctx.tables[cache.group], ctx.strides[cache.group]
-        q_abs = ws.get("latent.q", (T, H, r + rd), self.dtype)
         rope = self.position.spec
-        kernels.latent_prepare(q_abs, pages, proj, 0, -1 if s.shares_cache else nq + ng, q_lat, self.norm_w,
+        kernels.latent_prepare(q_abs, pages, proj, 0, -1 if s.shares_cache else nq + ng, None, self.norm_w,
                                self.position.frequencies(), ctx.positions, ctx.req_of_token, table, stride, H, d, rd, r,
                                rope.rotary_dim, s.norm_eps, rope.magnitude, ctx.err)
         # one key/value head over the cached rows: keys are the whole row, values its first kv_rank channels
         o_lat = ws.get("latent.o_lat", (T, H, r), self.dtype)
         latent_attend(o_lat, q_abs, pages, ctx, table, stride, cache.page_size, s.window, s.scale, self.sink)
-        # back out of the latent space, head by head: o[h] = o_lat[h] . W_uv,h^T
-        o_heads = ws.get("latent.o_heads", (H, T, dv), self.dtype)
-        batched_product(o_heads, o_lat.transpose(0, 1), self.w_uv)
+        # back out of the latent space, head by head: o[h] = o_lat[h] . W_uv,h^T, written where the output
+        # projection reads it; the gate then works in place
         inner = ws.get("latent.inner", (T, H * dv), self.dtype)
+        o_heads = inner.view(T, H, dv).transpose(0, 1)                                # [H, T, dv] view
+        batched_product(o_heads, o_lat.transpose(0, 1), self.w_uv)
         if s.gate:
             kernels.gate_sigmoid(inner, o_heads, proj[:, nq:nq + ng])
-        else:
-            inner.view(T, H, dv).copy_(o_heads.transpose(0, 1))
         out = ws.get("latent.out", (T, s.hidden), ctx.branch_dtype or self.dtype)
         linear(out, inner, self.w_o, ctx.err)
         return out

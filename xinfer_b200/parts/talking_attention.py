@@ -130,6 +130,14 @@ class TalkingAttention(Mixer):
         mma = (USE_TENSOR_CORES and self.dtype == torch.bfloat16 and out.stride(0) % 2 == 0 and out.data_ptr() % 4 == 0
                and kernels.attn_talking_mma_tile(nh, nkv, d, dv, longest) > 0)
         bq = kernels.attn_talking_mma_tile(nh, nkv, d, dv, longest) if mma else kernels.attn_talking_tile(nh, d, dv, longest)
+        if bq <= 0 and not s.talking_heads and out_scale == 1.0 and out.is_contiguous():
+            # no mix across heads: a head needs no other head in its block, and the kernel with one warp per
+            # (token, head) takes any number of heads of any size (a silent entry of score 0 is a sink of zeros)
+            if s.sink and getattr(self, "_zero_sink", None) is None:
+                self._zero_sink = torch.zeros(nh, dtype=torch.float32, device=self.device)
+            kernels.attention_plain(out.view(T, nh, dv), q, cache["k"], cache["v"], ctx.positions, ctx.req_of_token, table,
+                                    stride, s.window, s.scale, ctx.err, sink=self._zero_sink if s.sink else None)
+            return
         if bq <= 0:
             raise kernels.KernelError(f"attention with {nh} heads of {d}/{dv} channels does not fit the kernel's tile")
         parts, part_o, part_ml = 1, None, None
