@@ -99,7 +99,9 @@ XB_EXPORT int xb_latent_prepare(int dtype, void* q_abs, void* cache, const void*
     const size_t smem = (size_t)rot * sizeof(float);
     if (smem > 48 * 1024) return (int)cudaErrorInvalidValue;
     const int work = q_lat != nullptr ? nh * (rank + rd) : (nh * rd > rank + rd ? nh * rd : rank + rd);
-    const int threads = work >= 4096 ? 512 : (work >= 1024 ? 256 : 128);
+    // small blocks: a token's work is a few thousand elements behind a chain of dependent steps (angles, a block-wide
+    // sum), so many resident blocks hide more than many threads per block
+    const int threads = work >= 16384 ? 256 : 128;
 #define XB_GO(T)                                                                                                        \
     latent_prepare_kernel<T><<<tokens, threads, smem, stream>>>((T*)q_abs, (T*)cache, (const T*)proj, row_len, q_off,  \
         kv_off, (const T*)q_lat, ql_ts, ql_hs, norm_w, inv_freq, positions, req_of_token, block_table, table_stride,   \

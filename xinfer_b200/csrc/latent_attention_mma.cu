@@ -7,15 +7,18 @@
 //
 //   a. the tile's cached rows to shared memory by 16-byte asynchronous copies, one tile ahead (two buffers);
 //      rows outside the request are zero-filled;
-//   b. S = Q K^T: the four warps of a row group share the dk channels (16-channel steps w, w + 4, ...) and each
-//      forms a partial score of all 64 keys - eight independent accumulator tiles per warp; the four partial
-//      scores go to shared memory as float32;
-//   c. every warp sums its row group's partial scores in the layout of an A operand, applies scale, causal mask and
-//      window, and keeps the running maximum and sum of its rows (the four warps of a row group compute the
-//      same numbers); a head's sink enters as the start of maximum and sum;
-//   d. O <- O * correction + P V: the four warps of a row group take the value columns in turn (8-column
-//      tiles c, c + 4, c + 8, ...), so a row's accumulators are spread over four warps and a latent of 512
+//   b. S = Q K^T: the warps of a row group take 16 (or 8) keys each; a warp runs over the dk channels in four
+//      interleaved streams with accumulators of their own (eight independent accumulator tiles, so that no
+//      product waits for the one before it) and adds them at the end; the scores go to shared memory as float32;
+//   c. every warp reads its row group's scores in the layout of an A operand, scales them (into the base-2
+//      domain: weights are exp2), masks them where the tile touches a causal or window edge (tiles that every
+//      row of the block sees whole skip the masks), and keeps the running maximum and sum of its rows (the four
+//      warps of a row group compute the same numbers); a head's sink enters as the start of maximum and sum;
+//   d. O <- O * correction + P V: the warps of a row group take the value columns in turn (8-column tiles
+//      c, c + CW, c + 2 CW, ...), so a row's accumulators are spread over the warps and a latent of 512
 //      channels fits in registers.
+// A row group has four warps, or eight for wide latents (the block then has up to 16 warps over the same tiles
+// in shared memory: the tiles allow one block per SM, and more warps hide each other's waits).
 //
 // With `parts` > 1 (single tokens over long contexts) a row's key tiles are dealt out to `parts` blocks, which
 // leave unnormed sums, maxima and denominators in scratch; attn_latent_merge_kernel joins them.
@@ -45,7 +48,7 @@ struct LatentMmaArgs {
 
 __host__ __device__ inline size_t latent_mma_smem(int dk, int rg) {
     const size_t ld = dk + 8;
-    return (size_t)(16 * rg + 2 * LM_BK) * ld * 2 + (size_t)4 * 16 * rg * LM_LDS * 4;
+    return (size_t)(16 * rg + 2 * LM_BK) * ld * 2 + (size_t)16 * rg * LM_LDS * 4;
 }
 
 __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
@@ -53,15 +56,16 @@ __device__ __forceinline__ uint32_t pack_bf16(float a, float b) {
     return *reinterpret_cast<uint32_t*>(&t);
 }
 
-template <int MAXNT /* 8-column value tiles per warp */>
-__global__ void __launch_bounds__(256) attn_latent_mma_kernel(__nv_bfloat16* __restrict__ out,
+template <int MAXNT /* 8-column value tiles per warp */, int CW /* warps of a row group: 4 or 8 */>
+__global__ void __launch_bounds__(64 * CW) attn_latent_mma_kernel(__nv_bfloat16* __restrict__ out,
                                                               const __nv_bfloat16* __restrict__ q,
                                                               const __nv_bfloat16* __restrict__ cache, LatentMmaArgs a) {
     extern __shared__ __align__(16) unsigned char smraw[];
     __shared__ int s_entry, s_tile;
     const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
     const int H = a.nh, dk = a.dk, rank = a.rank, R = 16 * a.rg;
-    const int rgi = warp >> 2, cw = warp & 3;               // row group and column warp
+    const int rgi = warp / CW, cw = warp % CW;               // row group and column warp
+    constexpr int KW = LM_BK / CW;                          // keys of a warp in Q K^T: 16 or 8
     if (tid == 0) {
         int tile = blockIdx.x, found = -1;
         for (int b = 0; b < a.num_entries; ++b) {
@@ -107,11 +111,17 @@ __global__ void __launch_bounds__(256) attn_latent_mma_kernel(__nv_bfloat16* __r
     auto fetch = [&](int t, int buf) {
         const int k0 = k_begin + t * LM_BK;
         __nv_bfloat16* dst = Ks + (size_t)buf * LM_BK * ld;
-        for (int r = warp; r < LM_BK; r += nwarps) {
+        // the pages of this warp's rows (r = warp, warp + nwarps, ...), one lane each: the lookups wait together
+        int my_page = -2;
+        {
+            const int j = k0 + warp + lane * nwarps;
+            if (warp + lane * nwarps < LM_BK && j <= p_hi) my_page = table[j / a.page_size];
+        }
+        for (int r = warp, i = 0; r < LM_BK; r += nwarps, ++i) {
             const int j = k0 + r;
+            const int page = __shfl_sync(0xffffffffu, my_page, i);
             const __nv_bfloat16* src = nullptr;
             if (j <= p_hi) {
-                const int page = table[j / a.page_size];
                 if (page < 0 || page >= a.num_pages) {
                     if (lane == 0) atomicOr(a.err, XB_ERR_BAD_PAGE);
                 } else {
@@ -137,7 +147,7 @@ __global__ void __launch_bounds__(256) attn_latent_mma_kernel(__nv_bfloat16* __r
         m[i] = -INFINITY;
         l[i] = 0.f;
         if (valid && a.sink != nullptr && part == 0) {      // the entry without a key: exp(sink - m) with m = sink
-            m[i] = a.sink[(row0 + r) % H];
+            m[i] = a.sink[(row0 + r) % H] * 1.4426950408889634f;    // maxima are kept in the base-2 domain
             l[i] = 1.f;
         }
     }
@@ -159,73 +169,128 @@ __global__ void __launch_bounds__(256) attn_latent_mma_kernel(__nv_bfloat16* __r
         const __nv_bfloat16* Kt = Ks + (size_t)buf * LM_BK * ld;
         const int k0 = k_begin + t * LM_BK;
 
-        // b. this warp's share of the channels, all 64 keys: a partial score tile
+        // b. scores of this warp's keys (16, or 8 with eight warps to a row group): four streams over the channels,
+        //    each with accumulators of its own
         {
-            float s[8][4];
+            constexpr int NT = KW / 8;     // 8-key tiles of this warp
+            float s[4][NT][4];
 #pragma unroll
-            for (int n = 0; n < 8; ++n) s[n][0] = s[n][1] = s[n][2] = s[n][3] = 0.f;
+            for (int u = 0; u < 4; ++u)
+#pragma unroll
+                for (int n = 0; n < NT; ++n) s[u][n][0] = s[u][n][1] = s[u][n][2] = s[u][n][3] = 0.f;
             const int mi = lane >> 3, rr = lane & 7;
             const uint32_t qa = smem_addr(Qs + (size_t)(rgi * 16 + (mi & 1) * 8 + rr) * ld + (mi >> 1) * 8);
-            const uint32_t ka = smem_addr(Kt + (size_t)((mi >> 1) * 8 + rr) * ld + (mi & 1) * 8);
-            for (int ks = cw; ks < dk / 16; ks += 4) {
-                uint32_t af[4];
-                ldmatrix_x4(af, qa + ks * 32);
+            const int steps = dk / 16;
+            int ks = 0;
+            if (NT == 2) {
+                // one load brings 16 keys x 16 channels: the B operands of two key tiles for one step
+                const uint32_t ka = smem_addr(Kt + (size_t)(cw * KW + (mi >> 1) * 8 + rr) * ld + (mi & 1) * 8);
+                for (; ks + 4 <= steps; ks += 4) {
 #pragma unroll
-                for (int kb = 0; kb < 4; ++kb) {
-                    uint32_t bf[4];
-                    ldmatrix_x4(bf, ka + (uint32_t)(kb * 16 * ld * 2) + ks * 32);
-                    mma_bf16(s[2 * kb], af, bf[0], bf[1]);
-                    mma_bf16(s[2 * kb + 1], af, bf[2], bf[3]);
+                    for (int u = 0; u < 4; ++u) {
+                        uint32_t af[4], bf[4];
+                        ldmatrix_x4(af, qa + (ks + u) * 32);
+                        ldmatrix_x4(bf, ka + (ks + u) * 32);
+                        mma_bf16(s[u][0], af, bf[0], bf[1]);
+                        mma_bf16(s[u][NT - 1], af, bf[2], bf[3]);
+                    }
+                }
+                for (; ks < steps; ++ks) {
+                    uint32_t af[4], bf[4];
+                    ldmatrix_x4(af, qa + ks * 32);
+                    ldmatrix_x4(bf, ka + ks * 32);
+                    mma_bf16(s[0][0], af, bf[0], bf[1]);
+                    mma_bf16(s[0][NT - 1], af, bf[2], bf[3]);
+                }
+            } else {
+                // one load brings 8 keys x 32 channels: the B operands of one key tile for two steps
+                const uint32_t ka = smem_addr(Kt + (size_t)(cw * KW + rr) * ld + mi * 8);
+                for (; ks + 4 <= steps; ks += 4) {
+#pragma unroll
+                    for (int u = 0; u < 2; ++u) {
+                        uint32_t a0[4], a1[4], bf[4];
+                        ldmatrix_x4(a0, qa + (ks + 2 * u) * 32);
+                        ldmatrix_x4(a1, qa + (ks + 2 * u + 1) * 32);
+                        ldmatrix_x4(bf, ka + (ks + 2 * u) * 32);
+                        mma_bf16(s[2 * u][0], a0, bf[0], bf[1]);
+                        mma_bf16(s[2 * u + 1][0], a1, bf[2], bf[3]);
+                    }
+                }
+                for (; ks + 2 <= steps; ks += 2) {
+                    uint32_t a0[4], a1[4], bf[4];
+                    ldmatrix_x4(a0, qa + ks * 32);
+                    ldmatrix_x4(a1, qa + (ks + 1) * 32);
+                    ldmatrix_x4(bf, ka + ks * 32);
+                    mma_bf16(s[0][0], a0, bf[0], bf[1]);
+                    mma_bf16(s[1][0], a1, bf[2], bf[3]);
+                }
+                if (ks < steps) {          // an odd last step: the load's second half lies in the row's padding and is not used
+                    uint32_t a0[4], bf[4];
+                    ldmatrix_x4(a0, qa + ks * 32);
+                    ldmatrix_x4(bf, ka + ks * 32);
+                    mma_bf16(s[0][0], a0, bf[0], bf[1]);
                 }
             }
-            float* srow = Ss + ((size_t)cw * R + rgi * 16 + (lane >> 2)) * LM_LDS + 2 * quad;
+            float* srow = Ss + (size_t)(rgi * 16 + (lane >> 2)) * LM_LDS + cw * KW + 2 * quad;
 #pragma unroll
-            for (int n = 0; n < 8; ++n) {
-                *reinterpret_cast<float2*>(srow + n * 8) = make_float2(s[n][0], s[n][1]);
-                *reinterpret_cast<float2*>(srow + 8 * LM_LDS + n * 8) = make_float2(s[n][2], s[n][3]);
+            for (int n = 0; n < NT; ++n) {
+                float c[4];
+#pragma unroll
+                for (int e = 0; e < 4; ++e) c[e] = (s[0][n][e] + s[1][n][e]) + (s[2][n][e] + s[3][n][e]);
+                *reinterpret_cast<float2*>(srow + n * 8) = make_float2(c[0], c[1]);
+                *reinterpret_cast<float2*>(srow + 8 * LM_LDS + n * 8) = make_float2(c[2], c[3]);
             }
         }
         __syncthreads();
 
-        // c. mask, running maximum, weights of this thread's two rows in the layout of an A operand
+        // c. running maximum and weights of this thread's two rows in the layout of an A operand (base-2 domain)
+        // every row of the block sees every key of the tile: no masks
+        const bool whole = k0 + LM_BK - 1 <= p_lo && (a.window <= 0 || k0 > p_hi - a.window) && nrows == R;
+        const float sc2 = a.scale * 1.4426950408889634f;
         float p[2][16];
         float corr[2];
 #pragma unroll
         for (int i = 0; i < 2; ++i) {
             const float* srow = Ss + (size_t)(rgi * 16 + (lane >> 2) + 8 * i) * LM_LDS;
             float mx = -INFINITY;
+            if (whole) {
 #pragma unroll
-            for (int kk = 0; kk < 4; ++kk)
+                for (int kk = 0; kk < 4; ++kk)
 #pragma unroll
-                for (int hf = 0; hf < 2; ++hf) {
-                    const int col = kk * 16 + hf * 8 + 2 * quad;
-                    float2 v = *reinterpret_cast<const float2*>(srow + col);
-#pragma unroll
-                    for (int c = 1; c < 4; ++c) {
-                        const float2 u = *reinterpret_cast<const float2*>(srow + (size_t)c * R * LM_LDS + col);
-                        v.x += u.x;
-                        v.y += u.y;
+                    for (int hf = 0; hf < 2; ++hf) {
+                        const float2 v = *reinterpret_cast<const float2*>(srow + kk * 16 + hf * 8 + 2 * quad);
+                        const float x0 = v.x * sc2, x1 = v.y * sc2;
+                        p[i][kk * 4 + hf * 2] = x0;
+                        p[i][kk * 4 + hf * 2 + 1] = x1;
+                        mx = fmaxf(mx, fmaxf(x0, x1));
                     }
-                    const int j = k0 + col;
-                    const bool see0 = j <= rpos[i] && (a.window <= 0 || j > rpos[i] - a.window);
-                    const bool see1 = j + 1 <= rpos[i] && (a.window <= 0 || j + 1 > rpos[i] - a.window);
-                    const float x0 = see0 ? v.x * a.scale : -INFINITY, x1 = see1 ? v.y * a.scale : -INFINITY;
-                    p[i][kk * 4 + hf * 2] = x0;
-                    p[i][kk * 4 + hf * 2 + 1] = x1;
-                    mx = fmaxf(mx, fmaxf(x0, x1));
-                }
+            } else {
+                // keys this row sees within the tile: columns lo .. hi
+                const int hi = rpos[i] - k0;
+                const int lo = a.window > 0 ? rpos[i] - a.window + 1 - k0 : -0x40000000;
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        const int col = kk * 16 + hf * 8 + 2 * quad;
+                        const float2 v = *reinterpret_cast<const float2*>(srow + col);
+                        const float x0 = (col >= lo && col <= hi) ? v.x * sc2 : -INFINITY;
+                        const float x1 = (col + 1 >= lo && col + 1 <= hi) ? v.y * sc2 : -INFINITY;
+                        p[i][kk * 4 + hf * 2] = x0;
+                        p[i][kk * 4 + hf * 2 + 1] = x1;
+                        mx = fmaxf(mx, fmaxf(x0, x1));
+                    }
+            }
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
             mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
             const float m_new = fmaxf(m[i], mx);
             const float base = m_new == -INFINITY ? 0.f : m_new;     // nothing seen yet: every weight is zero
-            corr[i] = expf(m[i] - base);
+            corr[i] = exp2f(m[i] - base);
             float sum = 0.f;
 #pragma unroll
             for (int e = 0; e < 16; ++e) {
-                // the weight as the tensor core will see it (rounded), so that the denominator sums what is multiplied
-                const float w = __bfloat162float(__float2bfloat16_rn(expf(p[i][e] - base)));
-                p[i][e] = w;
-                sum += w;
+                p[i][e] = exp2f(p[i][e] - base);
+                sum += p[i][e];
             }
             sum += __shfl_xor_sync(0xffffffffu, sum, 1);
             sum += __shfl_xor_sync(0xffffffffu, sum, 2);
@@ -253,7 +318,7 @@ __global__ void __launch_bounds__(256) attn_latent_mma_kernel(__nv_bfloat16* __r
             const uint32_t va = smem_addr(Kt + (size_t)(kp * 32 + lane) * ld);
 #pragma unroll
             for (int n = 0; n < MAXNT; ++n) {
-                const int nt = cw + 4 * n;
+                const int nt = cw + CW * n;
                 if (nt < ntiles_v) {
                     uint32_t vf[4];
                     ldmatrix_x4_trans(vf, va + nt * 16);
@@ -275,7 +340,7 @@ __global__ void __launch_bounds__(256) attn_latent_mma_kernel(__nv_bfloat16* __r
             float* po = a.part_o + (grow * a.parts + part) * rank;
 #pragma unroll
             for (int n = 0; n < MAXNT; ++n) {
-                const int nt = cw + 4 * n;
+                const int nt = cw + CW * n;
                 if (nt < ntiles_v) *reinterpret_cast<float2*>(po + nt * 8 + 2 * quad) = make_float2(o[n][2 * i], o[n][2 * i + 1]);
             }
             if (cw == 0 && quad == 0) {
@@ -287,7 +352,7 @@ __global__ void __launch_bounds__(256) attn_latent_mma_kernel(__nv_bfloat16* __r
             __nv_bfloat16* orow = out + grow * rank;
 #pragma unroll
             for (int n = 0; n < MAXNT; ++n) {
-                const int nt = cw + 4 * n;
+                const int nt = cw + CW * n;
                 if (nt < ntiles_v)
                     *reinterpret_cast<__nv_bfloat162*>(orow + nt * 8 + 2 * quad) =
                         __floats2bfloat162_rn(o[n][2 * i] * inv, o[n][2 * i + 1] * inv);
@@ -296,7 +361,7 @@ __global__ void __launch_bounds__(256) attn_latent_mma_kernel(__nv_bfloat16* __r
     }
 }
 
-// out[row] = sum_p part_o[row, p] e^(m_p - M) / sum_p l_p e^(m_p - M),  M = max_p m_p
+// out[row] = sum_p part_o[row, p] 2^(m_p - M) / sum_p l_p 2^(m_p - M),  M = max_p m_p  (maxima in the base-2 domain)
 __global__ void attn_latent_merge_kernel(__nv_bfloat16* __restrict__ out, const float* __restrict__ part_o,
                                          const float* __restrict__ part_ml, int parts, int rank) {
     const size_t row = blockIdx.x;
@@ -305,14 +370,14 @@ __global__ void attn_latent_merge_kernel(__nv_bfloat16* __restrict__ out, const 
     float L = 0.f;
     for (int p = 0; p < parts; ++p) {
         const float mp = part_ml[(row * parts + p) * 2];
-        if (mp > -INFINITY) L += part_ml[(row * parts + p) * 2 + 1] * expf(mp - M);
+        if (mp > -INFINITY) L += part_ml[(row * parts + p) * 2 + 1] * exp2f(mp - M);
     }
     const float inv = L > 0.f ? 1.f / L : 0.f;
     for (int c = threadIdx.x; c < rank; c += blockDim.x) {
         float acc = 0.f;
         for (int p = 0; p < parts; ++p) {
             const float mp = part_ml[(row * parts + p) * 2];
-            if (mp > -INFINITY) acc += part_o[(row * parts + p) * rank + c] * expf(mp - M);
+            if (mp > -INFINITY) acc += part_o[(row * parts + p) * rank + c] * exp2f(mp - M);
         }
         out[row * rank + c] = __float2bfloat16_rn(acc * inv);
     }
@@ -345,18 +410,25 @@ XB_EXPORT int xb_attn_latent_mma(void* out, const void* q, const void* cache, co
     // every entry's rows are cut into tiles of their own: at most one ragged tile per entry
     const long long tiles = ((long long)tokens * nh + R - 1) / R + num_entries;
     const size_t smem = latent_mma_smem(dk, rg);
-    const dim3 grid((unsigned)tiles, (unsigned)parts), block(128 * rg);
-    const int ntw = (rank / 8 + 3) / 4;      // value tiles per warp
-#define XB_GO(N)                                                                                                     \
+    // eight warps to a row group where the latent is wide (more warps to hide each other's waits over the same tiles
+    // in shared memory), four where a warp would be left with less than two value tiles
+    const int cw = rank >= 128 ? 8 : 4;
+    const dim3 grid((unsigned)tiles, (unsigned)parts), block(32 * cw * rg);
+    const int ntw = (rank / 8 + cw - 1) / cw;      // value tiles per warp
+#define XB_GO(N, C)                                                                                                  \
     do {                                                                                                             \
-        cudaFuncSetAttribute(attn_latent_mma_kernel<N>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);     \
-        attn_latent_mma_kernel<N><<<grid, block, smem, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)q,       \
-                                                                 (const __nv_bfloat16*)cache, a);                    \
+        cudaFuncSetAttribute(attn_latent_mma_kernel<N, C>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);  \
+        attn_latent_mma_kernel<N, C><<<grid, block, smem, stream>>>((__nv_bfloat16*)out, (const __nv_bfloat16*)q,    \
+                                                                    (const __nv_bfloat16*)cache, a);                 \
     } while (0)
-    if (ntw <= 2) XB_GO(2);
-    else if (ntw <= 4) XB_GO(4);
-    else if (ntw <= 8) XB_GO(8);
-    else XB_GO(16);
+    if (cw == 8) {
+        if (ntw <= 2) XB_GO(2, 8);
+        else if (ntw <= 4) XB_GO(4, 8);
+        else XB_GO(8, 8);
+    } else {
+        if (ntw <= 2) XB_GO(2, 4);
+        else XB_GO(4, 4);
+    }
 #undef XB_GO
     int rc = xb_launch_status();
     if (rc != 0 || parts == 1) return rc;
