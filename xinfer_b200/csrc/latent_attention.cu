@@ -24,7 +24,7 @@ __global__ void latent_prepare_kernel(T* __restrict__ q_abs, T* __restrict__ cac
                                       const float* __restrict__ inv_freq, const int* __restrict__ positions,
                                       const int* __restrict__ req_of_token, const int* __restrict__ block_table,
                                       int table_stride, int nh, int d, int rd, int rank, int rot, int page_size,
-                                      int num_pages, float eps, float rot_mag, int* err) {
+                                      int num_pages, float eps, float rot_mag, int pairs, int* err) {
     extern __shared__ float sm[];
     __shared__ float scratch[33];
     const int half = rot / 2;
@@ -49,15 +49,29 @@ __global__ void latent_prepare_kernel(T* __restrict__ q_abs, T* __restrict__ cac
             q_abs[((size_t)t * nh + h) * dk + c] = q_lat[(size_t)t * ql_ts + (size_t)h * ql_hs + c];
         }
     }
-    for (int i = threadIdx.x; i < nh * rd; i += blockDim.x) {
-        const int h = i / rd, e = i % rd;
-        const T* qr = row + q_off + (size_t)h * (d + rd) + d;
-        float v = to_f32<T>(qr[e]);
-        if (e < rot) {
-            const float o = to_f32<T>(qr[e ^ 1]);
-            v = (e & 1) ? fmaf(v, cs[e >> 1], o * sn[e >> 1]) : fmaf(v, cs[e >> 1], -o * sn[e >> 1]);
+    if (pairs) {
+        // bfloat16 rows whose rotated parts start on 4-byte boundaries: a pair of neighbours per access
+        const int hp = rd / 2;
+        for (int i = threadIdx.x; i < nh * hp; i += blockDim.x) {
+            const int h = i / hp, pr = i % hp;
+            const __nv_bfloat162 in = *reinterpret_cast<const __nv_bfloat162*>(
+                reinterpret_cast<const __nv_bfloat16*>(row) + q_off + (size_t)h * (d + rd) + d + 2 * pr);
+            float2 v = __bfloat1622float2(in);
+            if (2 * pr < rot) v = make_float2(fmaf(v.x, cs[pr], -v.y * sn[pr]), fmaf(v.y, cs[pr], v.x * sn[pr]));
+            *reinterpret_cast<__nv_bfloat162*>(reinterpret_cast<__nv_bfloat16*>(q_abs) + ((size_t)t * nh + h) * dk + rank + 2 * pr) =
+                __floats2bfloat162_rn(v.x, v.y);
         }
-        q_abs[((size_t)t * nh + h) * dk + rank + e] = from_f32<T>(v);
+    } else {
+        for (int i = threadIdx.x; i < nh * rd; i += blockDim.x) {
+            const int h = i / rd, e = i % rd;
+            const T* qr = row + q_off + (size_t)h * (d + rd) + d;
+            float v = to_f32<T>(qr[e]);
+            if (e < rot) {
+                const float o = to_f32<T>(qr[e ^ 1]);
+                v = (e & 1) ? fmaf(v, cs[e >> 1], o * sn[e >> 1]) : fmaf(v, cs[e >> 1], -o * sn[e >> 1]);
+            }
+            q_abs[((size_t)t * nh + h) * dk + rank + e] = from_f32<T>(v);
+        }
     }
     if (kv_off < 0 || b < 0) return;
     const int page = block_table[(size_t)b * table_stride + pos / page_size];
@@ -105,7 +119,9 @@ XB_EXPORT int xb_latent_prepare(int dtype, void* q_abs, void* cache, const void*
 #define XB_GO(T)                                                                                                        \
     latent_prepare_kernel<T><<<tokens, threads, smem, stream>>>((T*)q_abs, (T*)cache, (const T*)proj, row_len, q_off,  \
         kv_off, (const T*)q_lat, ql_ts, ql_hs, norm_w, inv_freq, positions, req_of_token, block_table, table_stride,   \
-        nh, d, rd, rank, rot, page_size, num_pages, eps, rot_mag, err)
+        nh, d, rd, rank, rot, page_size, num_pages, eps, rot_mag, pairs, err)
+    const int pairs = (dtype == XB_BF16 && !((row_len | q_off | d | rd | rank) & 1) &&
+                       !(((uintptr_t)proj | (uintptr_t)q_abs) & 3)) ? 1 : 0;
     if (dtype == XB_F32) XB_GO(float);
     else XB_GO(__nv_bfloat16);
 #undef XB_GO
@@ -127,27 +143,29 @@ __global__ void gate_sigmoid_kernel(T* out, const T* heads, long long h_ts, long
     out[i] = from_f32<T>(o / (1.f + expf(-g)));
 }
 
-// eight bfloat16 elements per thread with 16-byte accesses (dv and every stride a multiple of 8, pointers aligned)
-__global__ void gate_sigmoid_bf16x8_kernel(__nv_bfloat16* __restrict__ out, const __nv_bfloat16* heads, long long h_ts,
+// eight bfloat16 elements per thread with 16-byte accesses (dv and every stride a multiple of 8, pointers aligned);
+// grid (pieces of a token's row, tokens)
+__global__ void gate_sigmoid_bf16x8_kernel(__nv_bfloat16* out, const __nv_bfloat16* heads, long long h_ts,
                                            long long h_hs, const __nv_bfloat16* __restrict__ gate, long long g_ts, int nh,
-                                           int dv, size_t nvec) {
-    const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
-    if (i >= nvec) return;
-    const size_t w = (size_t)nh * dv / 8;
-    const size_t t = i / w, c = (i % w) * 8;
-    const int h = (int)(c / dv), v = (int)(c % dv);
-    const uint4 pg = *reinterpret_cast<const uint4*>(gate + t * g_ts + c);
-    const uint4 po = *reinterpret_cast<const uint4*>(heads + t * h_ts + (size_t)h * h_hs + v);
-    const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&pg);
-    const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&po);
-    uint4 res;
-    __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
+                                           int dv, int tokens) {
+    const int w = nh * dv;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
+    if (c >= w) return;
+    const int h = c / dv, v = c - h * dv;
+    for (int t = blockIdx.y; t < tokens; t += gridDim.y) {
+        const uint4 pg = *reinterpret_cast<const uint4*>(gate + (size_t)t * g_ts + c);
+        const uint4 po = *reinterpret_cast<const uint4*>(heads + (size_t)t * h_ts + (size_t)h * h_hs + v);
+        const __nv_bfloat162* g2 = reinterpret_cast<const __nv_bfloat162*>(&pg);
+        const __nv_bfloat162* o2 = reinterpret_cast<const __nv_bfloat162*>(&po);
+        uint4 res;
+        __nv_bfloat162* r2 = reinterpret_cast<__nv_bfloat162*>(&res);
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-        const float2 g = __bfloat1622float2(g2[k]), o = __bfloat1622float2(o2[k]);
-        r2[k] = __floats2bfloat162_rn(o.x / (1.f + expf(-g.x)), o.y / (1.f + expf(-g.y)));
+        for (int k = 0; k < 4; ++k) {
+            const float2 g = __bfloat1622float2(g2[k]), o = __bfloat1622float2(o2[k]);
+            r2[k] = __floats2bfloat162_rn(o.x / (1.f + expf(-g.x)), o.y / (1.f + expf(-g.y)));
+        }
+        *reinterpret_cast<uint4*>(out + (size_t)t * w + c) = res;
     }
-    *reinterpret_cast<uint4*>(out + t * w * 8 + c) = res;
 }
 
 XB_EXPORT int xb_gate_sigmoid(int dtype, void* out, const void* heads, long long h_ts, long long h_hs, const void* gate,
@@ -156,9 +174,11 @@ XB_EXPORT int xb_gate_sigmoid(int dtype, void* out, const void* heads, long long
     if (n == 0) return 0;
     if (dtype == XB_BF16 && dv % 8 == 0 && h_ts % 8 == 0 && h_hs % 8 == 0 && g_ts % 8 == 0 &&
         !(((uintptr_t)out | (uintptr_t)heads | (uintptr_t)gate) & 15)) {
-        const size_t nvec = n / 8;
-        gate_sigmoid_bf16x8_kernel<<<(unsigned)((nvec + 255) / 256), 256, 0, stream>>>(
-            (__nv_bfloat16*)out, (const __nv_bfloat16*)heads, h_ts, h_hs, (const __nv_bfloat16*)gate, g_ts, nh, dv, nvec);
+        const int vecs = nh * dv / 8;
+        const int threads = vecs >= 256 ? 256 : 64;
+        const dim3 grid((unsigned)((vecs + threads - 1) / threads), (unsigned)(tokens < 65535 ? tokens : 65535));
+        gate_sigmoid_bf16x8_kernel<<<grid, threads, 0, stream>>>(
+            (__nv_bfloat16*)out, (const __nv_bfloat16*)heads, h_ts, h_hs, (const __nv_bfloat16*)gate, g_ts, nh, dv, tokens);
         return xb_launch_status();
     }
     const unsigned blocks = (unsigned)((n + 255) / 256);

@@ -530,7 +530,8 @@ def dufitar_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, h
     sets = 4
 
     def record(name, nbytes, run, like=None):
-        us = _loop_time_us(lambda: [run(i) for i in range(sets)]) / sets
+        # replayed from a CUDA graph: several of these kernels are shorter than the host's share of a launch
+        us = _graph_time_us(lambda: [run(i) for i in range(sets)], sets)
         rec = {"kernel": name, "tokens": tokens, "bytes": nbytes, "us": round(us, 1), "gbs": round(nbytes / us / 1e3, 1)}
         if hbm_gbs:
             rec["frac_of_floor"] = round(rec["gbs"] / hbm_gbs, 3)
