@@ -236,11 +236,11 @@ def dufitar_config(z: dict, lat: dict, layers: int, vocab: int) -> dict:
     d = z["head_dim"]
     attn = dict(type="attention", mlp=dict(kind="dense", ff=z["intermediate"]),
                 mixer=dict(heads=z["heads"], kv_heads=z["kv_heads"], dim=d, vdim=d, scale=d ** -0.5, mask=dict(size=COMPARE_WINDOW),
-                           rot=dict(dims=d // 2, base=500000.0, scaling=dict(factor=4.0, original=8192, fast=32.0, slow=1.0))))
+                           rot=dict(dims=d // 2, base=1000000.0, scaling=dict(factor=8.0, original=8192, fast=16.0, slow=2.0))))
 
     def latent(kv_from=None):
         m = dict(heads=z["heads"], dim=d, rot_dim=lat["rot_dim"], vdim=d, kv_rank=lat["kv_rank"],
-                 scale=(d + lat["rot_dim"]) ** -0.5, mask=dict(size=COMPARE_WINDOW), rot=dict(dims=lat["rot_dim"], base=250000.0))
+                 scale=(d + lat["rot_dim"]) ** -0.5, mask=dict(size=COMPARE_WINDOW), rot=dict(dims=lat["rot_dim"], base=100000.0))
         if kv_from is not None:
             m["kv_from"] = kv_from
         return dict(type="latent_attention", mixer=m, mlp=dict(kind="dense", ff=z["intermediate"]))
@@ -248,7 +248,7 @@ def dufitar_config(z: dict, lat: dict, layers: int, vocab: int) -> dict:
     out = []
     for i in range(layers):      # attention, latent, attention, latent reading the rows of the latent layer before it
         out.append(attn if i % 2 == 0 else latent(i - 2 if i % 4 == 3 else None))
-    return dict(architecture="Dufitar", vocab=vocab, width=z["hidden"], norm=dict(eps=1e-6), residual_mult=0.7,
+    return dict(architecture="Dufitar", vocab=vocab, width=z["hidden"], norm=dict(eps=1e-6), residual_mult=0.5,
                 embedding=dict(scale=2.0), layers=out)
 
 

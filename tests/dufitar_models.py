@@ -53,7 +53,7 @@ TINY_D: Dict[str, tuple] = {
     # several pages, a latent layer of its own beside one that is shared twice
     "D3": (dict(architecture="Dufitar", vocab=120, width=96, norm=dict(eps=1e-6), residual_mult=0.8, embedding=dict(scale=1.5),
                 layers=[
-        _with(_attn(4, 2, 32, 32, 0.6, 50, dict(dims=16, base=20000.0, scaling=_yarn(4.0, 128, 32.0, 1.0))), 160),
+        _with(_attn(4, 2, 32, 32, 0.6, 50, dict(dims=16, base=20000.0, scaling=_yarn(3.0, 128, 20.0, 1.0))), 160),
         _with(_latent(4, 32, 16, 32, 48, 0.5, 70, 5000.0), 128),
         _with(_attn(8, 1, 16, 16, 0.9, 23, dict(dims=16, base=100.0)), 64),
         _with(_latent(2, 16, 16, 24, 48, 0.6, 45, 5000.0, kv_from=1), 128),
@@ -67,6 +67,14 @@ TINY_D: Dict[str, tuple] = {
         _with(_latent(3, 6, 2, 10, 14, 1.1, 13, 900.0), 37),
         _with(_attn(2, 2, 18, 22, 0.7, 200, dict(dims=2, base=10.0)), None),
     ]), 24, 16),
+    # wide heads and a wide latent: the widest tiles of the tensor-core kernels (heads of 128 channels, a latent whose
+    # value columns are shared out among eight warps), windows of several key tiles
+    "D5": (dict(architecture="Dufitar", vocab=200, width=128, norm=dict(eps=1e-6), residual_mult=0.9, embedding=dict(scale=1.2),
+                layers=[
+        _with(_latent(3, 32, 16, 48, 128, 0.4, 150, 7000.0), 96),
+        _with(_attn(2, 1, 128, 128, 0.3, 100, dict(dims=64, base=40000.0, scaling=_yarn(2.5, 96, 12.0, 1.0))), 192),
+        _with(_latent(2, 16, 16, 16, 128, 0.5, 66, 7000.0, kv_from=0), None),
+    ]), 25, 16),
 }
 
 

@@ -104,10 +104,10 @@ def test_random_folder_holds_the_declared_tensors(tmp_path):
 
 @pytest.mark.parametrize("rot", [
     dict(dims=8, base=1000.0, scaling=dict(factor=8.0, original=64, fast=16.0, slow=2.0)),
-    dict(dims=48, base=500000.0, scaling=dict(factor=4.0, original=512, fast=32.0, slow=1.0)),
+    dict(dims=40, base=80000.0, scaling=dict(factor=6.0, original=256, fast=24.0, slow=1.5)),
     dict(dims=6, base=3000.0, scaling=dict(factor=5.0, original=40, fast=10.0, slow=3.0)),
     dict(dims=2, base=10.0, scaling=dict(factor=3.0, original=8, fast=4.0, slow=1.0)),     # hi == lo: the 0.001 floor
-    dict(dims=16, base=250000.0),
+    dict(dims=12, base=70000.0),
 ])
 def test_scaled_frequencies_equal_the_plain_rule(rot):
     from xinfer_b200.parts.rope import inv_frequencies

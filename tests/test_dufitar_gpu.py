@@ -52,7 +52,7 @@ def test_dynamic_tanh_with_scaled_and_normed_branch(x_dtype, branch_dtype, out_d
     br = _rand(rows, dim, seed=2, scale=3.0).to(branch_dtype) if branch_dtype is not None else None
     alpha, w, b = _rand(seed=3).abs().float() + 0.3, _rand(dim, seed=4).float(), _rand(dim, seed=5).float()
     ba, bw, bb = _rand(seed=6).abs().float() + 0.2, _rand(dim, seed=7).float(), _rand(dim, seed=8).float()
-    scale = 0.7
+    scale = 0.55
     s = x.double()
     if br is not None:
         v = br.double()
@@ -311,7 +311,8 @@ def _latent_qr(n, H, dk, seed, sharp=1.0):
 
 
 @pytest.mark.parametrize("dtype,tensor_cores", [(torch.float32, False), (torch.bfloat16, False), (torch.bfloat16, True)])
-@pytest.mark.parametrize("H,dk,rank", [(3, 24, 20), (4, 32, 16), (5, 80, 64), (16, 48, 40), (2, 576, 512), (40, 32, 24)])
+@pytest.mark.parametrize("H,dk,rank", [(3, 24, 20), (4, 32, 16), (5, 96, 72), (16, 48, 40), (2, 576, 512), (40, 32, 24),
+                                       (4, 160, 128), (3, 272, 256), (1, 144, 136)])
 @pytest.mark.parametrize("sink,window", [(True, None), (False, 19), (True, 70)])
 def test_latent_attention_equals_plain_for_unequal_entries(dtype, tensor_cores, H, dk, rank, sink, window):
     """Prompt portions of several lengths and starts beside single tokens, pages in a shuffled order."""
@@ -429,7 +430,8 @@ def test_window_attention_runs_on_the_attention_backend_and_equals_the_general_k
 # ---------------------------------------------------------------------------------------------
 # whole models: every way of cutting, pages used again, layer by layer, generation
 # ---------------------------------------------------------------------------------------------
-LENGTHS = {"D1": [70, 45, 130, 33], "D2": [97, 41, 260, 150], "D3": [170, 1, 75, 58], "D4": [90, 2, 51, 140]}
+LENGTHS = {"D1": [70, 45, 130, 33], "D2": [97, 41, 260, 150], "D3": [170, 1, 75, 58], "D4": [90, 2, 51, 140],
+           "D5": [200, 37, 3, 111]}
 
 
 def _row_error(got, want):
@@ -451,7 +453,7 @@ def _tolerance(dtype, ref, cfg=None, w=None, p=None):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["D1", "D2", "D3", "D4"])
+@pytest.mark.parametrize("name", ["D1", "D2", "D3", "D4", "D5"])
 def test_every_way_of_cutting_gives_the_plain_logits(name, dtype, tmp_path):
     folder = make_folder(str(tmp_path / "model"), name, torch.float32 if dtype == "float32" else torch.bfloat16)
     ps = prompts(name, LENGTHS[name])

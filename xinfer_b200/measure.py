@@ -542,9 +542,9 @@ def dufitar_kernels(*, hidden: int = 4096, heads: int = 32, kv_heads: int = 8, h
     xs = [torch.randn(tokens, hidden, device=device) for _ in range(sets)]
     bs = [torch.randn(tokens, hidden, device=device) for _ in range(sets)]
     os_ = [torch.empty(tokens, hidden, dtype=torch.bfloat16, device=device) for _ in range(sets)]
-    alpha, w, b = torch.tensor(0.7, device=device), torch.randn(hidden, device=device), torch.randn(hidden, device=device)
+    alpha, w, b = torch.tensor(0.9, device=device), torch.randn(hidden, device=device), torch.randn(hidden, device=device)
     record("Dynamic Tanh of the branch + scaled residual sum + Dynamic Tanh", tokens * hidden * (4 + 4 + 4 + 2),
-           lambda i: kernels.dyt_norm(os_[i], xs[i], alpha, w, b, err, branch=bs[i], branch_scale=0.7, branch_norm=(alpha, w, b),
+           lambda i: kernels.dyt_norm(os_[i], xs[i], alpha, w, b, err, branch=bs[i], branch_scale=0.5, branch_norm=(alpha, w, b),
                                       sum_out=xs[i]), "residual sum + RMSNorm")
     del xs, bs, os_
     gus = [bf(tokens, 2 * intermediate) for _ in range(sets)]
